@@ -1,0 +1,107 @@
+"""ctypes binding of the in-tree sm_100a library (``_lib/libpithb200.so``).
+
+The library has a plain C ABI (raw device pointers + a CUDA stream handle), so it is loaded with
+ctypes rather than through torch's extension machinery: builds take seconds and the shared object
+travels with the source tree. :func:`lib` raises if the library is missing, so a GPU run can never
+silently fall back to eager PyTorch.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p, c_float
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libpithb200.so"
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel reported a bounded-wait timeout or a capacity overflow through the status word."""
+
+
+STATUS_NAMES = {
+    1: "timeout in TMA producer",
+    2: "timeout in MMA issuer",
+    3: "timeout in epilogue",
+    4: "timeout waiting for a peer",
+    5: "receive-buffer capacity exceeded",
+    6: "timeout draining in-flight copies",
+}
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        raise NativeLibraryMissing(
+            f"{_LIB_PATH} not found: run `python -m pithtrain_b200.build` (or __graft_entry__.build())"
+        )
+    L = ctypes.CDLL(str(_LIB_PATH))
+    _declare(L)
+    return L
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    def sig(name, argtypes, restype=c_int):
+        if hasattr(L, name):
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+
+    P, I, LL, F = c_void_p, c_int, c_longlong, c_float
+    sig("pt_status_fetch_and_clear", [])
+    sig("pt_sm_count", [])
+    sig(
+        "pt_gemm_bf16",
+        [P, P, P, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, P, I, I, LL, I, I, I, I, I, P],
+    )
+    for name, args in _ELEMENTWISE_SIGS.items():
+        sig(name, [_CT[a] for a in args])
+
+
+_CT = {"P": c_void_p, "I": c_int, "L": c_longlong, "F": c_float}
+
+# name -> compact argument signature (P pointer, I int, L long long, F float); filled by ops modules
+_ELEMENTWISE_SIGS: dict[str, str] = {}
+
+
+def register_sig(name: str, args: str) -> None:
+    _ELEMENTWISE_SIGS[name] = args
+    if lib.cache_info().currsize:
+        L = lib()
+        if hasattr(L, name):
+            fn = getattr(L, name)
+            fn.argtypes = [_CT[a] for a in args]
+            fn.restype = c_int
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def check_status() -> None:
+    """Synchronise and raise if any kernel recorded a timeout / overflow since the last check."""
+    v = lib().pt_status_fetch_and_clear()
+    if v > 0:
+        raise KernelStatusError(STATUS_NAMES.get(v, f"status {v}"))
+    if v < 0:
+        raise RuntimeError(f"status word unavailable ({v})")

@@ -1,0 +1,178 @@
+"""bf16 GEMMs on the tcgen05 kernel family (dense, M-grouped, K-grouped) and their fp32 oracles.
+
+Layout vocabulary: an operand is "K-major" when its reduction dimension is contiguous in memory and
+"MN-major" when it is strided. The kernel reads either, so the wrappers below never transpose:
+
+* ``gemm_nt(x[M,K], w[N,K])``        forward  ``x @ w.T``        (both K-major)
+* ``gemm_nn(dy[M,N], w[N,K])``       dgrad    ``dy @ w``         (B MN-major)
+* ``gemm_tn(dy[M,N], x[M,K])``       wgrad    ``dy.T @ x``       (both MN-major)
+
+Grouped variants take ``offs`` (int32 ``[G+1]`` device tensor of row offsets, group sizes multiples
+of 16 for the K-grouped form); nothing is read back to the host.
+Counterparts in the reference: pithtrain/operators/grouped_linear.py:18-55 (F.grouped_mm) and the
+dense ``nn.Linear`` calls.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+
+DENSE, MGROUP, KGROUP = 0, 1, 2
+
+# Module-level switches used by tests and tuning runs.
+USE_TMA_STORE = True
+FORCE_BN = 0
+
+
+def _launch(a, b, d, mode, M, N, K, a_mn, b_mn, a_shape, lda, b_shape, ldb, d_rows, ldd,
+            offs=None, num_groups=0, b_group_rows=0, d_group_stride=0, accumulate=False,
+            max_ctas=0):
+    L = _native.lib()
+    out_fp32 = 1 if d.dtype == torch.float32 else 0
+    rc = L.pt_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, M, N, K, int(a_mn), int(b_mn),
+        a_shape[0], a_shape[1], lda, b_shape[0], b_shape[1], ldb, d_rows, ldd,
+        None if offs is None else offs.data_ptr(), num_groups, b_group_rows, d_group_stride,
+        out_fp32, int(accumulate), int(USE_TMA_STORE), FORCE_BN, max_ctas, _native.stream_ptr(),
+    )
+    _native.check(rc, "pt_gemm_bf16")
+
+
+def _chk2d(t: torch.Tensor, name: str):
+    assert t.dim() == 2 and t.stride(1) == 1, f"{name} must be row-major 2-D, got {t.shape} {t.stride()}"
+    assert t.dtype == torch.bfloat16, f"{name} must be bf16"
+    assert t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0, f"{name} must be 16-byte aligned"
+
+
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``x[M,K] @ w[N,K].T -> [M,N]``."""
+    if not x.is_cuda:
+        r = x.float() @ w.float().t()
+        if out is None:
+            return r.to(out_dtype)
+        out.copy_(out.float() + r if accumulate else r)
+        return out
+    _chk2d(x, "x"); _chk2d(w, "w")
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _launch(x, w, out, DENSE, M, N, K, False, False, (M, K), x.stride(0), (N, K), w.stride(0),
+            M, out.stride(0), accumulate=accumulate)
+    return out
+
+
+def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``dy[M,N] @ w[N,K] -> [M,K]`` (reduction over N; ``w`` is read MN-major)."""
+    if not dy.is_cuda:
+        r = dy.float() @ w.float()
+        if out is None:
+            return r.to(out_dtype)
+        out.copy_(out.float() + r if accumulate else r)
+        return out
+    _chk2d(dy, "dy"); _chk2d(w, "w")
+    M, N = dy.shape
+    K = w.shape[1]
+    assert w.shape[0] == N
+    if out is None:
+        out = torch.empty((M, K), dtype=out_dtype, device=dy.device)
+    # GEMM view: D[M, K] = A[M, red=N] * B[red=N, K]
+    _launch(dy, w, out, DENSE, M, K, N, False, True, (M, N), dy.stride(0), (N, K), w.stride(0),
+            M, out.stride(0), accumulate=accumulate)
+    return out
+
+
+def gemm_tn(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None,
+            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``dy[M,N].T @ x[M,K] -> [N,K]`` (reduction over rows; both operands read MN-major)."""
+    if not dy.is_cuda:
+        r = dy.float().t() @ x.float()
+        if out is None:
+            return r.to(out_dtype)
+        out.copy_(out.float() + r if accumulate else r)
+        return out
+    _chk2d(dy, "dy"); _chk2d(x, "x")
+    M, N = dy.shape
+    K = x.shape[1]
+    assert x.shape[0] == M
+    if out is None:
+        assert not accumulate
+        out = torch.empty((N, K), dtype=out_dtype, device=dy.device)
+    _launch(dy, x, out, DENSE, N, K, M, True, True, (M, N), dy.stride(0), (M, K), x.stride(0),
+            N, out.stride(0), accumulate=accumulate)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# grouped
+# ------------------------------------------------------------------------------------------------
+def _group_loop(offs: torch.Tensor):
+    o = offs.tolist()
+    return [(g, o[g], o[g + 1]) for g in range(len(o) - 1)]
+
+
+def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows ``[offs[g], offs[g+1])`` of ``x[R,K]`` times ``w[g][N,K].T`` -> ``out[R,N]``.
+
+    Rows at or beyond ``offs[-1]`` are left untouched.
+    """
+    G, N, K = w.shape
+    if out is None:
+        out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
+    if not x.is_cuda:
+        for g, a, b in _group_loop(offs):
+            out[a:b] = (x[a:b].float() @ w[g].float().t()).to(out.dtype)
+        return out
+    _chk2d(x, "x")
+    assert w.is_contiguous() and w.dtype == torch.bfloat16 and offs.dtype == torch.int32
+    R = x.shape[0]
+    _launch(x, w, out, MGROUP, R, N, K, False, False, (R, K), x.stride(0), (G * N, K), K,
+            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N)
+    return out
+
+
+def grouped_gemm_nn(dy: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows of group g of ``dy[R,N]`` times ``w[g][N,K]`` -> ``out[R,K]`` (expert dgrad)."""
+    G, N, K = w.shape
+    if out is None:
+        out = torch.empty((dy.shape[0], K), dtype=torch.bfloat16, device=dy.device)
+    if not dy.is_cuda:
+        for g, a, b in _group_loop(offs):
+            out[a:b] = (dy[a:b].float() @ w[g].float()).to(out.dtype)
+        return out
+    _chk2d(dy, "dy")
+    assert w.is_contiguous() and w.dtype == torch.bfloat16 and offs.dtype == torch.int32
+    assert N % 64 == 0, "reduction dim of a grouped dgrad must be a multiple of 64"
+    R = dy.shape[0]
+    _launch(dy, w, out, MGROUP, R, K, N, False, True, (R, N), dy.stride(0), (G * N, K), K,
+            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N)
+    return out
+
+
+def grouped_gemm_tn(dy: torch.Tensor, x: torch.Tensor, offs: torch.Tensor, out: torch.Tensor,
+                    accumulate: bool = True) -> torch.Tensor:
+    """``out[g] (+)= dy[rows_g].T @ x[rows_g]`` with ``out[G,N,K]`` (expert wgrad).
+
+    Group sizes must be multiples of 16; pad rows must be zero in ``dy`` (or ``x``).
+    """
+    G, N, K = out.shape
+    if not dy.is_cuda:
+        for g, a, b in _group_loop(offs):
+            r = dy[a:b].float().t() @ x[a:b].float()
+            out[g] = (out[g].float() + r if accumulate else r).to(out.dtype)
+        return out
+    _chk2d(dy, "dy"); _chk2d(x, "x")
+    assert out.is_contiguous() and offs.dtype == torch.int32
+    if not accumulate:
+        out.zero_()
+    R = dy.shape[0]
+    _launch(dy, x, out, KGROUP, N, K, 0, True, True, (R, N), dy.stride(0), (R, K), x.stride(0),
+            N, K, offs=offs, num_groups=G, d_group_stride=N * K, accumulate=True)
+    return out
