@@ -1,0 +1,357 @@
+// RMSNorm (with fused residual add) and fused per-head QK-RMSNorm + rotary embedding, forward and
+// backward. Memory-bound kernels: one 16-byte vector per thread per access, each tensor read once.
+// They replace the Inductor-generated stage-1 region of the reference
+// (pithtrain/models/qwen3_moe.py:156-168,188-202).
+#include "elementwise.cuh"
+#include "host_common.h"
+
+namespace pt {
+
+constexpr int NORM_THREADS = 256;
+
+// y = (x [+ res]) * rstd * w ; optionally writes h = x + res and rstd.
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int n_rows,
+                   int H, float eps, int w_plus_one) {
+  __shared__ float red[32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + (size_t)row * H;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        load8(xr + c * 8, v[i]);
+        if (res) {
+          float r[8];
+          load8(res + (size_t)row * H + c * 8, r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += r[e];
+          if (h_out) {
+            // round to bf16 first so the norm sees exactly the stored residual stream
+            store8(h_out + (size_t)row * H + c * 8, v[i]);
+            load8(h_out + (size_t)row * H + c * 8, v[i]);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+      }
+    }
+    ss = block_sum(ss, red);
+    float rstd = rsqrtf(ss / H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float wv[8], o[8];
+        load8(w + c * 8, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = v[i][e] * rstd * (w_plus_one ? (1.f + wv[e]) : wv[e]);
+        store8(y + (size_t)row * H + c * 8, o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) [+ dh_extra]; dw partial per CTA (fp32).
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dh_extra,
+                   const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ w,
+                   const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int n_rows, int H, int w_plus_one) {
+  __shared__ float red[32];
+  const int nvec = H / 8;
+  float dw[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dw[i][e] = 0.f;
+  for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    float rstd = rstd_in[row];
+    float xh[VPT][8], g[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float wv[8];
+        load8(h + (size_t)row * H + c * 8, xh[i]);
+        load8(dy + (size_t)row * H + c * 8, g[i]);
+        load8(w + c * 8, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[i][e] *= rstd;
+          dw[i][e] += g[i][e] * xh[i][e];
+          g[i][e] *= (w_plus_one ? (1.f + wv[e]) : wv[e]);
+          dot += g[i][e] * xh[i][e];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[i][e] - xh[i][e] * dot);
+        if (dh_extra) {
+          float ex[8];
+          load8(dh_extra + (size_t)row * H + c * 8, ex);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += ex[e];
+        }
+        store8(dx + (size_t)row * H + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      float* p = dw_partial + (size_t)blockIdx.x * H + c * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) p[e] = dw[i][e];
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Fused per-head RMSNorm (optional) + rotate-half RoPE for q and k, reading the fused qkv GEMM output.
+// One warp per (token, head). D in {64, 128}: PAIRS = D/64 rotation pairs per lane.
+// ----------------------------------------------------------------------------------------------
+template <int PAIRS>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                        __nv_bfloat16* __restrict__ k_out, const __nv_bfloat16* __restrict__ qw,
+                        const __nv_bfloat16* __restrict__ kw, const __nv_bfloat16* __restrict__ cosb,
+                        const __nv_bfloat16* __restrict__ sinb, const int* __restrict__ pos,
+                        float* __restrict__ rstd_q, float* __restrict__ rstd_k, int n_tokens, int S,
+                        int Hq, int Hkv, long long qkv_stride, float eps, int w_plus_one, int rot_dim) {
+  constexpr int D = PAIRS * 64;
+  const int half = D / 2;
+  const int lane = threadIdx.x & 31;
+  const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = Hq + Hkv;
+  if (warp_id >= (long long)n_tokens * heads) return;
+  const int tok = (int)(warp_id / heads), hd = (int)(warp_id % heads);
+  const bool is_q = hd < Hq;
+  const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + (size_t)hd * D;  // k heads follow q heads
+  __nv_bfloat16* dst = is_q ? q_out + ((size_t)tok * Hq + hd) * D : k_out + ((size_t)tok * Hkv + (hd - Hq)) * D;
+  const __nv_bfloat16* wn = is_q ? qw : kw;
+  const int p = pos ? pos[tok] : (tok % S);
+  float a[PAIRS], b[PAIRS];  // element i and its partner i + half
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PAIRS; ++j) {
+    int i = lane + 32 * j;
+    a[j] = __bfloat162float(src[i]);
+    b[j] = __bfloat162float(src[i + half]);
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  float rstd = 1.f;
+  if (wn) {
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / D + eps);
+    if (lane == 0) {
+      if (is_q) rstd_q[(size_t)tok * Hq + hd] = rstd;
+      else rstd_k[(size_t)tok * Hkv + (hd - Hq)] = rstd;
+    }
+  }
+  const int rhalf = rot_dim / 2;
+#pragma unroll
+  for (int j = 0; j < PAIRS; ++j) {
+    int i = lane + 32 * j;
+    float na = a[j] * rstd, nb = b[j] * rstd;
+    if (wn) {
+      float wa = __bfloat162float(wn[i]), wb = __bfloat162float(wn[i + half]);
+      if (w_plus_one) { wa += 1.f; wb += 1.f; }
+      na *= wa; nb *= wb;
+    }
+    // round like the unfused path (norm output is bf16 before the rotation)
+    na = __bfloat162float(__float2bfloat16(na));
+    nb = __bfloat162float(__float2bfloat16(nb));
+    float oa = na, ob = nb;
+    if (rot_dim == D) {
+      float c = __bfloat162float(cosb[(size_t)p * D + i]), s = __bfloat162float(sinb[(size_t)p * D + i]);
+      oa = na * c - nb * s;
+      ob = nb * c + na * s;
+    } else {
+      (void)rhalf;
+    }
+    dst[i] = __float2bfloat16(oa);
+    dst[i + half] = __float2bfloat16(ob);
+  }
+}
+
+template <int PAIRS>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+                        const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ dqkv,
+                        const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                        const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb,
+                        const int* __restrict__ pos, const float* __restrict__ rstd_q,
+                        const float* __restrict__ rstd_k, float* __restrict__ dw_partial,
+                        int n_tokens, int S, int Hq, int Hkv, long long qkv_stride, int w_plus_one) {
+  constexpr int D = PAIRS * 64;
+  const int half = D / 2;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int heads = Hq + Hkv;
+  const long long total = (long long)n_tokens * heads;
+  float dwq_a[PAIRS], dwq_b[PAIRS], dwk_a[PAIRS], dwk_b[PAIRS];
+#pragma unroll
+  for (int j = 0; j < PAIRS; ++j) dwq_a[j] = dwq_b[j] = dwk_a[j] = dwk_b[j] = 0.f;
+  for (long long warp_id = (long long)blockIdx.x * wpb + wib; warp_id < total;
+       warp_id += (long long)gridDim.x * wpb) {
+    const int tok = (int)(warp_id / heads), hd = (int)(warp_id % heads);
+    const bool is_q = hd < Hq;
+    const __nv_bfloat16* g = is_q ? dq + ((size_t)tok * Hq + hd) * D : dk + ((size_t)tok * Hkv + (hd - Hq)) * D;
+    const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + (size_t)hd * D;
+    __nv_bfloat16* dst = dqkv + (size_t)tok * qkv_stride + (size_t)hd * D;
+    const __nv_bfloat16* wn = is_q ? qw : kw;
+    const int p = pos ? pos[tok] : (tok % S);
+    float dna[PAIRS], dnb[PAIRS], xa[PAIRS], xb[PAIRS];
+    float rstd = 1.f;
+    if (wn) rstd = is_q ? rstd_q[(size_t)tok * Hq + hd] : rstd_k[(size_t)tok * Hkv + (hd - Hq)];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      int i = lane + 32 * j;
+      float ga = __bfloat162float(g[i]), gb = __bfloat162float(g[i + half]);
+      float c = __bfloat162float(cosb[(size_t)p * D + i]), s = __bfloat162float(sinb[(size_t)p * D + i]);
+      dna[j] = ga * c + gb * s;
+      dnb[j] = gb * c - ga * s;
+      if (wn) {
+        xa[j] = __bfloat162float(src[i]) * rstd;
+        xb[j] = __bfloat162float(src[i + half]) * rstd;
+        float wa = __bfloat162float(wn[i]), wb = __bfloat162float(wn[i + half]);
+        if (w_plus_one) { wa += 1.f; wb += 1.f; }
+        if (is_q) { dwq_a[j] += dna[j] * xa[j]; dwq_b[j] += dnb[j] * xb[j]; }
+        else { dwk_a[j] += dna[j] * xa[j]; dwk_b[j] += dnb[j] * xb[j]; }
+        dna[j] *= wa; dnb[j] *= wb;
+        dot += dna[j] * xa[j] + dnb[j] * xb[j];
+      }
+    }
+    if (wn) {
+      dot = warp_sum(dot) / D;
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        dna[j] = rstd * (dna[j] - xa[j] * dot);
+        dnb[j] = rstd * (dnb[j] - xb[j] * dot);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      int i = lane + 32 * j;
+      dst[i] = __float2bfloat16(dna[j]);
+      dst[i + half] = __float2bfloat16(dnb[j]);
+    }
+  }
+  if (qw && dw_partial) {
+    // reduce the per-warp weight-gradient partials across the block, one row of 2*D per CTA
+    __shared__ float sm[8][2 * 128 + 2 * 128];
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      int i = lane + 32 * j;
+      sm[wib][i] = dwq_a[j]; sm[wib][i + half] = dwq_b[j];
+      sm[wib][D + i] = dwk_a[j]; sm[wib][D + i + half] = dwk_b[j];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
+      float s = 0.f;
+      for (int wv = 0; wv < wpb; ++wv) s += sm[wv][c];
+      dw_partial[(size_t)blockIdx.x * 2 * D + c] = s;
+    }
+  }
+}
+
+}  // namespace pt
+
+using namespace pt;
+
+PT_API int pt_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
+                          float* rstd, int n_rows, int H, float eps, int w_plus_one, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_rows <= 0) return 0;
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * 4) return -1;
+  int vpt = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  int grid = n_rows < sm_count() * 8 ? n_rows : sm_count() * 8;
+#define LAUNCH(V)                                                                                     \
+  rmsnorm_fwd_kernel<V><<<grid, NORM_THREADS, 0, st>>>(                                               \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, \
+      (__nv_bfloat16*)h_out, rstd, n_rows, H, eps, w_plus_one)
+  switch (vpt) { case 1: LAUNCH(1); break; case 2: LAUNCH(2); break; case 3: LAUNCH(3); break; default: LAUNCH(4); }
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// dw_partial must hold [grid, H] floats where grid = pt_rmsnorm_bwd_grid(n_rows).
+PT_API int pt_rmsnorm_bwd_grid(int n_rows) {
+  int g = sm_count() * 4;
+  return n_rows < g ? (n_rows > 0 ? n_rows : 1) : g;
+}
+PT_API int pt_rmsnorm_bwd(const void* dy, const void* dh_extra, const void* h, const void* w,
+                          const float* rstd, void* dx, float* dw_partial, int n_rows, int H,
+                          int w_plus_one, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_rows <= 0) return 0;
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * 4) return -1;
+  int vpt = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  int grid = pt_rmsnorm_bwd_grid(n_rows);
+#define LAUNCH(V)                                                                                 \
+  rmsnorm_bwd_kernel<V><<<grid, NORM_THREADS, 0, st>>>(                                           \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dh_extra, (const __nv_bfloat16*)h,          \
+      (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, dw_partial, n_rows, H, w_plus_one)
+  switch (vpt) { case 1: LAUNCH(1); break; case 2: LAUNCH(2); break; case 3: LAUNCH(3); break; default: LAUNCH(4); }
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+PT_API int pt_qk_norm_rope_fwd(const void* qkv, void* q_out, void* k_out, const void* qw,
+                               const void* kw, const void* cosb, const void* sinb, const int* pos,
+                               float* rstd_q, float* rstd_k, int n_tokens, int S, int Hq, int Hkv,
+                               int D, long long qkv_stride, float eps, int w_plus_one, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_tokens <= 0) return 0;
+  if (D != 64 && D != 128) return -1;
+  long long warps = (long long)n_tokens * (Hq + Hkv);
+  int grid = (int)((warps + 7) / 8);
+  if (D == 128)
+    qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out,
+        (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb, (const __nv_bfloat16*)sinb, pos,
+        rstd_q, rstd_k, n_tokens, S, Hq, Hkv, qkv_stride, eps, w_plus_one, D);
+  else
+    qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out,
+        (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb, (const __nv_bfloat16*)sinb, pos,
+        rstd_q, rstd_k, n_tokens, S, Hq, Hkv, qkv_stride, eps, w_plus_one, D);
+  return (int)cudaGetLastError();
+}
+
+PT_API int pt_qk_norm_rope_bwd_grid() { return sm_count() * 4; }
+// dw_partial: [grid, 2*D] floats (q weight grads then k weight grads per row); may be null when qw is null.
+PT_API int pt_qk_norm_rope_bwd(const void* dq, const void* dk, const void* qkv, void* dqkv,
+                               const void* qw, const void* kw, const void* cosb, const void* sinb,
+                               const int* pos, const float* rstd_q, const float* rstd_k,
+                               float* dw_partial, int n_tokens, int S, int Hq, int Hkv, int D,
+                               long long qkv_stride, int w_plus_one, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_tokens <= 0) return 0;
+  if (D != 64 && D != 128) return -1;
+  int grid = pt_qk_norm_rope_bwd_grid();
+  if (D == 128)
+    qk_norm_rope_bwd_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv,
+        (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb,
+        (const __nv_bfloat16*)sinb, pos, rstd_q, rstd_k, dw_partial, n_tokens, S, Hq, Hkv, qkv_stride, w_plus_one);
+  else
+    qk_norm_rope_bwd_kernel<1><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv,
+        (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb,
+        (const __nv_bfloat16*)sinb, pos, rstd_q, rstd_k, dw_partial, n_tokens, S, Hq, Hkv, qkv_stride, w_plus_one);
+  return (int)cudaGetLastError();
+}

@@ -40,16 +40,25 @@ def _launch(a, b, d, mode, M, N, K, a_mn, b_mn, a_shape, lda, b_shape, ldb, d_ro
     _native.check(rc, "pt_gemm_bf16")
 
 
+def _native_ok(*ts: torch.Tensor) -> bool:
+    ok = all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+    if ok:
+        _native.lib()
+    return ok
+
+
 def _chk2d(t: torch.Tensor, name: str):
     assert t.dim() == 2 and t.stride(1) == 1, f"{name} must be row-major 2-D, got {t.shape} {t.stride()}"
     assert t.dtype == torch.bfloat16, f"{name} must be bf16"
     assert t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0, f"{name} must be 16-byte aligned"
 
 
+@torch.no_grad()
 def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+            accumulate: bool = False, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x[M,K] @ w[N,K].T -> [M,N]``."""
-    if not x.is_cuda:
+    out_dtype = out_dtype or x.dtype
+    if not _native_ok(x, w):
         r = x.float() @ w.float().t()
         if out is None:
             return r.to(out_dtype)
@@ -66,10 +75,12 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+@torch.no_grad()
 def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+            accumulate: bool = False, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``dy[M,N] @ w[N,K] -> [M,K]`` (reduction over N; ``w`` is read MN-major)."""
-    if not dy.is_cuda:
+    out_dtype = out_dtype or dy.dtype
+    if not _native_ok(dy, w):
         r = dy.float() @ w.float()
         if out is None:
             return r.to(out_dtype)
@@ -87,10 +98,12 @@ def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+@torch.no_grad()
 def gemm_tn(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None,
-            accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+            accumulate: bool = False, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``dy[M,N].T @ x[M,K] -> [N,K]`` (reduction over rows; both operands read MN-major)."""
-    if not dy.is_cuda:
+    out_dtype = out_dtype or dy.dtype
+    if not _native_ok(dy, x):
         r = dy.float().t() @ x.float()
         if out is None:
             return r.to(out_dtype)
@@ -116,6 +129,7 @@ def _group_loop(offs: torch.Tensor):
     return [(g, o[g], o[g + 1]) for g in range(len(o) - 1)]
 
 
+@torch.no_grad()
 def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
                     out: torch.Tensor | None = None) -> torch.Tensor:
     """Rows ``[offs[g], offs[g+1])`` of ``x[R,K]`` times ``w[g][N,K].T`` -> ``out[R,N]``.
@@ -124,8 +138,8 @@ def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
     """
     G, N, K = w.shape
     if out is None:
-        out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
-    if not x.is_cuda:
+        out = torch.empty((x.shape[0], N), dtype=x.dtype, device=x.device)
+    if not _native_ok(x, w):
         for g, a, b in _group_loop(offs):
             out[a:b] = (x[a:b].float() @ w[g].float().t()).to(out.dtype)
         return out
@@ -137,13 +151,14 @@ def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
     return out
 
 
+@torch.no_grad()
 def grouped_gemm_nn(dy: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
                     out: torch.Tensor | None = None) -> torch.Tensor:
     """Rows of group g of ``dy[R,N]`` times ``w[g][N,K]`` -> ``out[R,K]`` (expert dgrad)."""
     G, N, K = w.shape
     if out is None:
-        out = torch.empty((dy.shape[0], K), dtype=torch.bfloat16, device=dy.device)
-    if not dy.is_cuda:
+        out = torch.empty((dy.shape[0], K), dtype=dy.dtype, device=dy.device)
+    if not _native_ok(dy, w):
         for g, a, b in _group_loop(offs):
             out[a:b] = (dy[a:b].float() @ w[g].float()).to(out.dtype)
         return out
@@ -156,6 +171,7 @@ def grouped_gemm_nn(dy: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
     return out
 
 
+@torch.no_grad()
 def grouped_gemm_tn(dy: torch.Tensor, x: torch.Tensor, offs: torch.Tensor, out: torch.Tensor,
                     accumulate: bool = True) -> torch.Tensor:
     """``out[g] (+)= dy[rows_g].T @ x[rows_g]`` with ``out[G,N,K]`` (expert wgrad).
@@ -163,7 +179,7 @@ def grouped_gemm_tn(dy: torch.Tensor, x: torch.Tensor, offs: torch.Tensor, out: 
     Group sizes must be multiples of 16; pad rows must be zero in ``dy`` (or ``x``).
     """
     G, N, K = out.shape
-    if not dy.is_cuda:
+    if not _native_ok(dy, x):
         for g, a, b in _group_loop(offs):
             r = dy[a:b].float().t() @ x[a:b].float()
             out[g] = (out[g].float() + r if accumulate else r).to(out.dtype)

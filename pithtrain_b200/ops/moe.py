@@ -1,0 +1,317 @@
+"""Expert-side MoE compute: routing sort, row gather, SwiGLU, weighted combine, and the fused
+expert block with a hand-written backward.
+
+Layout. The expert rank receives ``n`` token rows ``x[n, H]``, their ``k`` routing weights
+``w[n, k]`` and local expert ids ``eids[n, k]`` (``-1`` marks a slot whose expert lives on another
+rank). :func:`route_sort` counting-sorts the ``n*k`` slots by expert into groups aligned to 16 rows
+and returns device-side ``offs[E+1]`` plus the two permutations; all buffers are sized from the
+static upper bound ``n*k + 16*E`` so no count is ever read back to the host (the reference syncs
+twice per layer here: pithtrain/operators/ep_dispatch.py:630-646,
+pithtrain/operators/token_scatter.py:227-264).
+
+:func:`moe_experts` then computes ``partial[t] = sum_j w[t,j] * down_e(act(gate_up_e(x[t])))`` — the
+routing weights are applied on the expert rank, so the tensor that travels back is one row per
+received token (the reference returns one row per (token, expert) pair and sums at home,
+pithtrain/models/qwen3_moe.py:229-245). Its backward never stores the per-slot expert outputs:
+the routing-weight gradient is recovered as ``<dgrad_of_down(d_out[t]), act>`` inside the SwiGLU
+backward kernel, which also emits the weight-scaled activation consumed by the down-projection
+wgrad.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from .. import _native
+from ..dualpipe.utils import WeightGradStore
+from . import gemm as G
+from .common import accumulate_grad, sp, use_native
+
+ALIGN = 16
+
+
+def sorted_capacity(n_slots: int, num_experts: int) -> int:
+    """Static row capacity of the expert-sorted layout for ``n_slots`` slots."""
+    cap = n_slots + ALIGN * num_experts
+    return (cap + 127) // 128 * 128
+
+
+# ------------------------------------------------------------------------------------------------
+# route_sort
+# ------------------------------------------------------------------------------------------------
+def route_sort_ref(eids: torch.Tensor, num_experts: int, r_cap: int):
+    n = eids.numel()
+    e = eids.view(-1).long()
+    valid = (e >= 0) & (e < num_experts)
+    counts = torch.bincount(e[valid], minlength=num_experts)
+    padded = (counts + ALIGN - 1) // ALIGN * ALIGN
+    offs = torch.zeros(num_experts + 1, dtype=torch.long, device=eids.device)
+    offs[1:] = padded.cumsum(0)
+    key = torch.where(valid, e, torch.full_like(e, num_experts))
+    order = torch.sort(key, stable=True).indices  # slots grouped by expert, slot order inside
+    sorted_key = key[order]
+    n_valid = int(valid.sum())
+    rank_in_group = torch.arange(n, device=eids.device) - torch.cat(
+        [torch.zeros(1, dtype=torch.long, device=eids.device), counts.cumsum(0)])[sorted_key.clamp(max=num_experts)]
+    row = offs[sorted_key.clamp(max=num_experts - 1)] + rank_in_group
+    row_of_slot = torch.full((n,), -1, dtype=torch.int32, device=eids.device)
+    slot_of_row = torch.full((r_cap,), -1, dtype=torch.int32, device=eids.device)
+    ord_v, row_v = order[:n_valid], row[:n_valid]
+    row_of_slot[ord_v] = row_v.int()
+    slot_of_row[row_v] = ord_v.int()
+    return offs.int(), row_of_slot, slot_of_row
+
+
+def route_sort(eids: torch.Tensor, num_experts: int, r_cap: Optional[int] = None,
+               n_valid: Optional[torch.Tensor] = None):
+    """Stable counting sort of slots by expert.
+
+    Returns ``offs[E+1]`` (int32), ``row_of_slot[n]`` (-1 for skipped slots) and ``slot_of_row[r_cap]``
+    (-1 for pad rows). ``n_valid`` optionally bounds the slots by a device-side count.
+    """
+    flat = eids.reshape(-1)
+    n = flat.numel()
+    if r_cap is None:
+        r_cap = sorted_capacity(n, num_experts)
+    if not flat.is_cuda:
+        if n_valid is not None:
+            flat = flat.clone()
+            flat[int(n_valid):] = -1
+        return route_sort_ref(flat, num_experts, r_cap)
+    L = _native.lib()
+    flat = flat.int() if flat.dtype != torch.int32 else flat
+    flat = flat.contiguous()
+    dev = flat.device
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    offs = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    row_of_slot = torch.empty(n, dtype=torch.int32, device=dev)
+    slot_of_row = torch.empty(r_cap, dtype=torch.int32, device=dev)
+    rc = L.pt_route_sort(flat.data_ptr(), None if n_valid is None else n_valid.data_ptr(), n, num_experts,
+                         ALIGN, counts.data_ptr(), offs.data_ptr(), row_of_slot.data_ptr(),
+                         slot_of_row.data_ptr(), r_cap, sp())
+    _native.check(rc, "pt_route_sort")
+    return offs, row_of_slot, slot_of_row
+
+
+# ------------------------------------------------------------------------------------------------
+# gather / combine / swiglu primitives (no autograd; used by the fused block and by other ops)
+# ------------------------------------------------------------------------------------------------
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, div: int = 1,
+                n_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dst[r] = src[idx[r] // div]``, zero rows where ``idx[r] < 0``; rows past ``n_rows`` undefined."""
+    R, H = idx.numel(), src.shape[-1]
+    if use_native(src) and H % 8 == 0 and src.stride(-1) == 1:
+        dst = torch.empty((R, H), dtype=src.dtype, device=src.device)
+        rc = _native.lib().pt_gather_rows(src.data_ptr(), idx.data_ptr(), div, dst.data_ptr(),
+                                          None if n_rows is None else n_rows.data_ptr(), R, H, src.stride(0), sp())
+        _native.check(rc, "pt_gather_rows")
+        return dst
+    i = idx.long()
+    out = src[(i.clamp(min=0) // div)]
+    return out * (i >= 0).unsqueeze(-1).to(src.dtype)
+
+
+def combine_rows(y: torch.Tensor, row_of_slot: torch.Tensor, k: int, w: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = residual[t] + sum_j w[t,j] * y[row_of_slot[t*k+j]]`` skipping negative rows."""
+    n = row_of_slot.numel() // k
+    H = y.shape[-1]
+    if use_native(y) and H % 8 == 0:
+        out = torch.empty((n, H), dtype=y.dtype, device=y.device)
+        wf = None if w is None else w.float().contiguous()
+        rc = _native.lib().pt_combine(y.data_ptr(), row_of_slot.data_ptr(), None if wf is None else wf.data_ptr(),
+                                      None if residual is None else residual.contiguous().data_ptr(),
+                                      out.data_ptr(), None, n, k, H, sp())
+        _native.check(rc, "pt_combine")
+        return out
+    r = row_of_slot.view(n, k).long()
+    rows = y[r.clamp(min=0)].float() * (r >= 0).unsqueeze(-1)
+    if w is not None:
+        rows = rows * w.float().view(n, k, 1)
+    out = rows.sum(1)
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(y.dtype)
+
+
+def _swiglu_math(g, u, alpha, limit):
+    if limit > 0:
+        gc = g.clamp(max=limit)
+        uc = u.clamp(min=-limit, max=limit)
+        return (uc + 1) * gc * torch.sigmoid(alpha * gc)
+    return torch.nn.functional.silu(g) * u
+
+
+def _split_gu(gu, interleaved):
+    I = gu.shape[-1] // 2
+    if interleaved:
+        return gu[..., 0::2], gu[..., 1::2]
+    return gu[..., :I], gu[..., I:]
+
+
+def swiglu_fwd(gu: torch.Tensor, n_rows: Optional[torch.Tensor] = None, interleaved: bool = False,
+               alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
+    R, I = gu.shape[0], gu.shape[1] // 2
+    if use_native(gu) and I % 8 == 0:
+        act = torch.empty((R, I), dtype=gu.dtype, device=gu.device)
+        rc = _native.lib().pt_swiglu_fwd(gu.data_ptr(), act.data_ptr(), None if n_rows is None else n_rows.data_ptr(),
+                                         R, I, int(interleaved), float(alpha), float(limit), sp())
+        _native.check(rc, "pt_swiglu_fwd")
+        return act
+    g, u = _split_gu(gu.float(), interleaved)
+    return _swiglu_math(g, u, alpha, limit).to(gu.dtype)
+
+
+def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor, row_w: Optional[torch.Tensor] = None,
+               n_rows: Optional[torch.Tensor] = None, interleaved: bool = False, alpha: float = 1.0,
+               limit: float = 0.0, want_act: bool = False, want_dw: bool = False):
+    """Returns ``(dgu, act_scaled or None, d_row_w or None)``; see the kernel comment for semantics."""
+    R, I = gu.shape[0], gu.shape[1] // 2
+    if use_native(gu) and I % 8 == 0:
+        dgu = torch.empty_like(gu)
+        act = torch.empty((R, I), dtype=gu.dtype, device=gu.device) if want_act else None
+        dw = torch.zeros(R, dtype=torch.float32, device=gu.device) if want_dw else None
+        rw = None if row_w is None else row_w.float().contiguous()
+        rc = _native.lib().pt_swiglu_bwd(gu.data_ptr(), dact.contiguous().data_ptr(), None if rw is None else rw.data_ptr(),
+                                         dgu.data_ptr(), None if act is None else act.data_ptr(),
+                                         None if dw is None else dw.data_ptr(),
+                                         None if n_rows is None else n_rows.data_ptr(), R, I, int(interleaved),
+                                         float(alpha), float(limit), sp())
+        _native.check(rc, "pt_swiglu_bwd")
+        return dgu, act, dw
+    with torch.enable_grad():
+        guf = gu.detach().float().requires_grad_()
+        g, u = _split_gu(guf, interleaved)
+        a = _swiglu_math(g, u, alpha, limit)
+        wt = torch.ones(R, device=gu.device) if row_w is None else row_w.float()
+        d = dact.float()
+        (dguf,) = torch.autograd.grad(a, guf, d * wt[:, None])
+    dw = (d * a.detach()).sum(-1) if want_dw else None
+    act = (a.detach() * wt[:, None]).to(gu.dtype) if want_act else None
+    return dguf.to(gu.dtype), act, dw
+
+
+def segment_sum(x: torch.Tensor, offs: torch.Tensor, num_groups: int) -> torch.Tensor:
+    """Per-group column sums ``[G, H]`` in fp32 of rows ``[offs[g], offs[g+1])`` (bias gradients)."""
+    R = x.shape[0]
+    row = torch.arange(R, device=x.device)
+    gid = torch.bucketize(row, offs[1:].long(), right=True)  # rows past offs[-1] -> G
+    out = torch.zeros((num_groups + 1, x.shape[1]), dtype=torch.float32, device=x.device)
+    out.index_add_(0, gid, x.float())
+    return out[:num_groups]
+
+
+def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
+    row = torch.arange(R, device=offs.device)
+    return torch.bucketize(row, offs[1:].long(), right=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# fused expert block
+# ------------------------------------------------------------------------------------------------
+class ExpertWeights:
+    """What :func:`moe_experts` needs from the owning module.
+
+    ``w1`` is the fused gate/up projection ``[E, 2I, H]`` (gate rows first, or interleaved), ``w2`` the
+    down projection ``[E, H, I]``; ``g1``/``g2`` return the gradient buffers to accumulate into.
+    ``b1``/``b2`` are optional per-expert biases (``[E, 2I]``, ``[E, H]``) as parameters.
+    """
+
+    def __init__(self, w1, w2, g1: Callable[[], torch.Tensor], g2: Callable[[], torch.Tensor],
+                 b1=None, b2=None, interleaved=False, alpha=1.0, limit=0.0):
+        self.w1, self.w2, self.g1, self.g2 = w1, w2, g1, g2
+        self.b1, self.b2 = b1, b2
+        self.interleaved, self.alpha, self.limit = interleaved, alpha, limit
+
+
+class _MoEExpertsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eids, ew: ExpertWeights, n_valid):
+        n, k = eids.shape
+        E = ew.w1.shape[0]
+        offs, row_of_slot, slot_of_row = route_sort(eids, E, n_valid=(None if n_valid is None else n_valid * k))
+        n_rows = offs[E:E + 1]
+        xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
+        gu = G.grouped_gemm_nt(xs, ew.w1, offs)
+        gid = None
+        if ew.b1 is not None:
+            gid = rows_group_id(offs, gu.shape[0]).clamp(max=E - 1)
+            gu = gu + ew.b1.detach()[gid].to(gu.dtype)
+        act = swiglu_fwd(gu, n_rows, ew.interleaved, ew.alpha, ew.limit)
+        y = G.grouped_gemm_nt(act, ew.w2, offs)
+        if ew.b2 is not None:
+            y = y + ew.b2.detach()[gid].to(y.dtype)
+        out = combine_rows(y, row_of_slot, k, w=w)
+        ctx.save_for_backward(x, w, gu, offs, row_of_slot, slot_of_row)
+        ctx.ew = ew
+        ctx.k = k
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        x, w, gu, offs, row_of_slot, slot_of_row = ctx.saved_tensors
+        ew, k = ctx.ew, ctx.k
+        E = ew.w1.shape[0]
+        n_rows = offs[E:E + 1]
+        d_out = d_out.contiguous()
+        dyg = gather_rows(d_out, slot_of_row, div=k, n_rows=n_rows)  # unscaled d_out per sorted row
+        da = G.grouped_gemm_nn(dyg, ew.w2, offs)
+        w_ext = torch.cat([w.reshape(-1).float(), w.new_zeros(1, dtype=torch.float32)])
+        row_w = w_ext[slot_of_row.long()]  # -1 (pad) picks the appended zero
+        dgu, act_s, d_row_w = swiglu_bwd(gu, da, row_w, n_rows, ew.interleaved, ew.alpha, ew.limit,
+                                         want_act=True, want_dw=True)
+        del da
+        if ew.b2 is not None:
+            # y = act @ W2.T + b2 ; the routing-weight gradient also sees the bias term
+            gid = rows_group_id(offs, gu.shape[0]).clamp(max=E - 1)
+            d_row_w = d_row_w + (dyg.float() * ew.b2.detach()[gid].float()).sum(-1)
+            accumulate_grad(ew.b2, segment_sum(dyg.float() * row_w[:, None], offs, E))
+        if ew.b1 is not None:
+            accumulate_grad(ew.b1, segment_sum(dgu, offs, E))
+        dw_ext = torch.cat([d_row_w, d_row_w.new_zeros(1)])
+        d_w = dw_ext[row_of_slot.long()].view(w.shape).to(w.dtype)
+        dxs = G.grouped_gemm_nn(dgu, ew.w1, offs)
+        d_x = combine_rows(dxs, row_of_slot, k) if ctx.needs_input_grad[0] else None
+        del dxs
+
+        def wgrad_fn(dyg=dyg, act_s=act_s, dgu=dgu, x=x, slot_of_row=slot_of_row, offs=offs, n_rows=n_rows):
+            G.grouped_gemm_tn(dyg, act_s, offs, ew.g2(), accumulate=True)
+            xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
+            G.grouped_gemm_tn(dgu, xs, offs, ew.g1(), accumulate=True)
+
+        if WeightGradStore.enabled:
+            WeightGradStore.put(wgrad_fn)
+        else:
+            wgrad_fn()
+        return d_x, d_w, None, None, None
+
+
+def moe_experts(x: torch.Tensor, w: torch.Tensor, eids: torch.Tensor, ew: ExpertWeights,
+                n_valid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weighted expert outputs for received tokens: ``out[t] = sum_j w[t,j] * expert_{eids[t,j]}(x[t])``."""
+    if not x.requires_grad and torch.is_grad_enabled():
+        x = x.detach().requires_grad_()
+    return _MoEExpertsFn.apply(x.contiguous(), w, eids, ew, n_valid)
+
+
+def moe_experts_ref(x, w, eids, w1, w2, b1=None, b2=None, interleaved=False, alpha=1.0, limit=0.0):
+    """Plain-autograd per-expert loop, the oracle for :func:`moe_experts`."""
+    n, k = eids.shape
+    out = torch.zeros_like(x, dtype=torch.float32)
+    for e in range(w1.shape[0]):
+        tok, slot = torch.where(eids == e)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok].float()
+        gu = xe @ w1[e].float().t()
+        if b1 is not None:
+            gu = gu + b1[e].float()
+        g, u = _split_gu(gu, interleaved)
+        a = _swiglu_math(g, u, alpha, limit)
+        y = a @ w2[e].float().t()
+        if b2 is not None:
+            y = y + b2[e].float()
+        out.index_add_(0, tok, y * w[tok, slot].float().unsqueeze(-1))
+    return out.to(x.dtype)

@@ -86,6 +86,20 @@ class Mesh4D:
                 if ranks == mine:
                     self.groups[axes] = g
 
+    def ensure_group(self, *axes: str):
+        """Group along ``axes``, created on first use (collective: all ranks must call it)."""
+        key = tuple(axes)
+        if key not in self.groups:
+            mine = self.ranks_along(key)
+            self.group_ranks[key] = mine
+            self.groups[key] = None
+            if dist.is_initialized() and self.world_size > 1:
+                for ranks in self.all_groups_along(key):
+                    g = dist.new_group(ranks=ranks) if len(ranks) > 1 else None
+                    if ranks == mine:
+                        self.groups[key] = g
+        return self.groups[key]
+
     def group(self, *axes: str):
         return self.groups.get(tuple(axes))
 
