@@ -51,34 +51,37 @@ def lib() -> ctypes.CDLL:
     return L
 
 
-def _declare(L: ctypes.CDLL) -> None:
-    def sig(name, argtypes, restype=c_int):
-        if hasattr(L, name):
-            fn = getattr(L, name)
-            fn.argtypes = argtypes
-            fn.restype = restype
-
-    P, I, LL, F = c_void_p, c_int, c_longlong, c_float
-    sig("pt_status_fetch_and_clear", [])
-    sig("pt_sm_count", [])
-    sig(
-        "pt_gemm_bf16",
-        [P, P, P, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, P, I, I, LL, I, I, I, I, I, P],
-    )
-    for name, args in _ELEMENTWISE_SIGS.items():
-        sig(name, [_CT[a] for a in args])
-
+SIGS = {
+    "pt_status_fetch_and_clear": "",
+    "pt_sm_count": "",
+    "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIP",
+    "pt_rmsnorm_fwd": "PPPPPPIIFIP",
+    "pt_rmsnorm_bwd_grid": "I",
+    "pt_rmsnorm_bwd": "PPPPPPPIIIP",
+    "pt_qk_norm_rope_fwd": "PPPPPPPPPPIIIIILFIP",
+    "pt_qk_norm_rope_bwd_grid": "",
+    "pt_qk_norm_rope_bwd": "PPPPPPPPPPPPIIIIILIP",
+    "pt_router_topk_fwd": "PIPPPIIIIIFP",
+    "pt_router_topk_bwd": "PPPPPPIIIIIIFP",
+    "pt_route_sort": "PPIIIPPPPIP",
+    "pt_gather_rows": "PPIPPIILP",
+    "pt_combine": "PPPPPPIIIP",
+    "pt_swiglu_fwd": "PPPIIIFFP",
+    "pt_swiglu_bwd": "PPPPPPPIIIFFP",
+    "pt_cross_entropy": "PPPIILIP",
+    "pt_scale_bf16": "PPLP",
+    "pt_sumsq_grid": "",
+    "pt_sumsq": "PILPP",
+    "pt_adamw": "PIPIPPLPFFFFFFFP",
+    "pt_muon_momentum": "PIPIPLFP",
+    "pt_axpby_bf16": "PPLFFP",
+}
 
 _CT = {"P": c_void_p, "I": c_int, "L": c_longlong, "F": c_float}
 
-# name -> compact argument signature (P pointer, I int, L long long, F float); filled by ops modules
-_ELEMENTWISE_SIGS: dict[str, str] = {}
 
-
-def register_sig(name: str, args: str) -> None:
-    _ELEMENTWISE_SIGS[name] = args
-    if lib.cache_info().currsize:
-        L = lib()
+def _declare(L: ctypes.CDLL) -> None:
+    for name, args in SIGS.items():
         if hasattr(L, name):
             fn = getattr(L, name)
             fn.argtypes = [_CT[a] for a in args]
@@ -93,9 +96,16 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+# Number of kernel launches issued through this module since it was last reset (bench bookkeeping).
+LAUNCHES = 0
+_LAUNCHES_PER_CALL = {"pt_route_sort": 3}
+
+
 def check(rc: int, what: str) -> None:
+    global LAUNCHES
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
+    LAUNCHES += _LAUNCHES_PER_CALL.get(what, 1)
 
 
 def check_status() -> None:

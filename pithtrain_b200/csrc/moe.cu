@@ -93,7 +93,8 @@ router_topk_fwd_kernel(const T* __restrict__ logits, float* __restrict__ probs,
   if (mode == 1) {
     // softmax over the k selected logits (picked_w[0] is the maximum)
     float s = 0.f;
-    for (int t = 0; t < k; ++t) { picked_w[t] = __expf(picked_w[t] - picked_w[0]); s += picked_w[t]; }
+    const float top = picked_w[0];
+    for (int t = 0; t < k; ++t) { picked_w[t] = __expf(picked_w[t] - top); s += picked_w[t]; }
     for (int t = 0; t < k; ++t) picked_w[t] = picked_w[t] / s * scale;
   } else {
     float mul = renorm ? scale / wsum : scale;

@@ -179,6 +179,7 @@ class FusedWeights:
                     p.data = view
                 if gviews[i] is not None:
                     p.main_grad = gviews[i]
+                p._fusion = (self, i)
         self.fused, self.fused_grad = fused, fused_grad
 
     def _in_place(self, tensors, fused) -> bool:

@@ -193,7 +193,18 @@ class FlatShardGroup:
         if self.flat_grad is None:
             return torch.zeros((), dtype=torch.float32)
         g = self.my_slice(self.flat_grad)
-        return g.float().pow(2).sum() / self.replica_size
+        if g.is_cuda and g.dtype in (torch.float32, torch.bfloat16) and g.numel() % 8 == 0:
+            from .. import _native
+
+            L = _native.lib()
+            part = torch.empty(L.pt_sumsq_grid(), dtype=torch.float64, device=g.device)
+            rc = L.pt_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), part.data_ptr(), _native.stream_ptr())
+            _native.check(rc, "pt_sumsq")
+            return part.sum().float() / self.replica_size
+        total = torch.zeros((), dtype=torch.float32, device=g.device)
+        for c in g.split(1 << 26):
+            total += c.float().pow(2).sum()
+        return total / self.replica_size
 
     def gather_params(self) -> None:
         """Publish the owners' updated regions to every rank of the shard group."""

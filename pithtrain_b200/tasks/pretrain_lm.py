@@ -128,7 +128,7 @@ def clip_grad_norm_(model: Optional[nn.Module] = None, max_norm: float = 1.0, no
 def model_flops_per_token(config, seq_len: int) -> float:
     """Training FLOPs per token: 6 x active matmul parameters (lm_head included, embedding lookup
     excluded) + causal attention 3 x 2*S*Hq*D per layer."""
-    from ..tools.memory_estimator.model_profile import active_matmul_params, attention_dims
+    from ..utils.model_stats import active_matmul_params, attention_dims
 
     p = active_matmul_params(config)
     hq, d_qk, d_v = attention_dims(config)
@@ -139,31 +139,16 @@ def model_flops_per_token(config, seq_len: int) -> float:
 # ------------------------------------------------------------------------------------------------
 # step
 # ------------------------------------------------------------------------------------------------
-def train_step(cfg: PretrainLMCfg) -> dict:
-    """One optimizer step. Returns the step's metrics (populated on every rank)."""
-    t = cfg.training
-    d = distributed
-    use_cuda = d.device.type == "cuda"
-    if t.nsys_start is not None and training.step == t.nsys_start and use_cuda:
-        torch.cuda.cudart().cudaProfilerStart()
-        torch.cuda.nvtx.range_push(
-            f"rank={d.rank}; pp={d.pp_rank}/{d.pp_size} dp={d.dp_rank}/{d.dp_size} cp={d.cp_rank}/{d.cp_size} "
-            f"ep={d.ep_rank}/{d.ep_size}; mbs={t.micro_batch_size} seq={t.sequence_length}")
-    if t.memory_profile_start is not None and training.step == t.memory_profile_start and use_cuda:
-        torch.cuda.memory._record_memory_history(max_entries=65536, stacks="python")
-
-    t0 = time.time()
-    ev0 = ev1 = None
-    if use_cuda:
-        torch.cuda.reset_peak_memory_stats()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-
+def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], labels: Optional[torch.Tensor]):
+    """Device-side part of a step: all micro-batches through the pipeline, gradient normalisation,
+    reduction, clipping, optimizer and scheduler steps, parameter all-gather. Nothing is read back to
+    the host. Returns ``(loss, gradient_norm)`` as device tensors (``loss`` is ``None`` off pp rank 0).
+    """
+    t, d = cfg.training, distributed
     model, optimizers, schedulers = training.model, training.optimizers, training.schedulers
     model.train()
     assert t.global_batch_size % (t.micro_batch_size * d.dp_size * d.ep_size) == 0
     accumulate_steps = t.global_batch_size // (t.micro_batch_size * d.dp_size * d.ep_size)
-    tokens, labels = get_global_batch(cfg, d.device)
 
     loss, _ = model.step(tokens, num_chunks=accumulate_steps, criterion=criterion, labels=labels, return_outputs=False)
 
@@ -198,6 +183,32 @@ def train_step(cfg: PretrainLMCfg) -> dict:
         g.gather_params()
         g.zero_grad()
     MoELoadBalanceLossTracker.reset()
+    return loss, gradient_norm
+
+
+def train_step(cfg: PretrainLMCfg) -> dict:
+    """One optimizer step. Returns the step's metrics (populated on every rank)."""
+    t = cfg.training
+    d = distributed
+    use_cuda = d.device.type == "cuda"
+    if t.nsys_start is not None and training.step == t.nsys_start and use_cuda:
+        torch.cuda.cudart().cudaProfilerStart()
+        torch.cuda.nvtx.range_push(
+            f"rank={d.rank}; pp={d.pp_rank}/{d.pp_size} dp={d.dp_rank}/{d.dp_size} cp={d.cp_rank}/{d.cp_size} "
+            f"ep={d.ep_rank}/{d.ep_size}; mbs={t.micro_batch_size} seq={t.sequence_length}")
+    if t.memory_profile_start is not None and training.step == t.memory_profile_start and use_cuda:
+        torch.cuda.memory._record_memory_history(max_entries=65536, stacks="python")
+
+    t0 = time.time()
+    ev0 = ev1 = None
+    if use_cuda:
+        torch.cuda.reset_peak_memory_stats()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+
+    tokens, labels = get_global_batch(cfg, d.device)
+    loss, gradient_norm = forward_backward_update(cfg, tokens, labels)
+    schedulers = training.schedulers
 
     device_ms = None
     if use_cuda:
