@@ -54,7 +54,7 @@ def lib() -> ctypes.CDLL:
 SIGS = {
     "pt_status_fetch_and_clear": "",
     "pt_sm_count": "",
-    "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIP",
+    "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIP",
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
     "pt_rmsnorm_bwd": "PPPPPPPIIIP",

@@ -41,6 +41,7 @@ struct GemmArgs {
   int out_fp32;
   int accumulate;
   int use_tma_store;
+  int epi;  // 0 staged coalesced rows, 1 direct per-thread rows, 2 TMA reduce-add when accumulating (else direct)
   int* err;
 };
 
@@ -143,7 +144,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (args.use_tma_store) tma_prefetch_desc(&tmD);
+    if (args.use_tma_store || args.epi == 2) tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, TMEM_COLS);
@@ -302,7 +303,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_store_commit();
           }
         }
-      } else {
+      } else if (args.epi == 2 && args.accumulate && (args.mode != GEMM_MGROUP || full_tile)) {
+        // ---- TMA reduce-add: stage a 32x(128 B) slab per warp, let the copy engine do D += slab
+        used_tma = true;
+        const int cols_per = args.out_fp32 ? 32 : 64;
+#pragma unroll 1
+        for (int cc = 0; cc * cols_per < BN; ++cc) {
+          if (ti.col0 + cc * cols_per >= args.N) break;
+          uint8_t* st = staging + (q * 2 + (cc & 1)) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          uint8_t* rowp = st + lane * 128;
+          if (args.out_fp32) {
+            uint32_t r0[32];
+            tmem_ld_32x32(taddr + cc * 32, r0);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+          } else {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + cc * 64, r0);
+            tmem_ld_32x32(taddr + cc * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v, w;
+              v.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+              w.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+              w.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+              w.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+              w.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+              *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = w;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (args.mode == GEMM_KGROUP)
+              tma_reduce_add_3d(&tmD, st, ti.col0 + cc * cols_per, ti.row0 + q * 32, (int)ti.d_off);
+            else
+              tma_reduce_add_2d(&tmD, st, ti.col0 + cc * cols_per, ti.row0 + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else if (args.epi != 0) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int col = ti.col0 + c * 32;
@@ -344,6 +393,76 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   v.z = pack_bf16x2(f[4], f[5]); v.w = pack_bf16x2(f[6], f[7]);
                   *reinterpret_cast<uint4*>(p + 8 * i) = v;
                 }
+              }
+            }
+          }
+        }
+      } else {
+        // ---- staged: registers -> swizzled smem slab -> coalesced 128-byte row segments in global
+        // (read-modify-write when accumulating). Handles ragged rows/columns and both output dtypes.
+        uint8_t* st = staging + q * 2 * 4096;
+        const int cols_per = args.out_fp32 ? 32 : 64;
+        const int sub_row = lane >> 3, chunk = lane & 7;
+#pragma unroll 1
+        for (int cc = 0; cc * cols_per < BN; ++cc) {
+          const int col_base = ti.col0 + cc * cols_per;
+          if (col_base >= args.N) break;
+          uint8_t* rowp = st + lane * 128;
+          __syncwarp();
+          if (args.out_fp32) {
+            uint32_t r0[32];
+            tmem_ld_32x32(taddr + cc * 32, r0);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+          } else {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + cc * 64, r0);
+            tmem_ld_32x32(taddr + cc * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v, w;
+              v.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+              w.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+              w.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+              w.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+              w.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+              *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = w;
+            }
+          }
+          __syncwarp();
+          const int elems_per_chunk = args.out_fp32 ? 4 : 8;
+          const int col = col_base + chunk * elems_per_chunk;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rloc = it * 4 + sub_row;
+            const int grow = ti.row0 + q * 32 + rloc;
+            if (grow < ti.row_end && col < args.N) {
+              uint4 v = *reinterpret_cast<const uint4*>(st + rloc * 128 + ((chunk ^ (rloc & 7)) << 4));
+              if (args.out_fp32) {
+                float* p = reinterpret_cast<float*>(args.D) + d_off + (long long)grow * args.ldd + col;
+                if (args.accumulate) {
+                  float4 o = *reinterpret_cast<const float4*>(p);
+                  v.x = __float_as_uint(__uint_as_float(v.x) + o.x); v.y = __float_as_uint(__uint_as_float(v.y) + o.y);
+                  v.z = __float_as_uint(__uint_as_float(v.z) + o.z); v.w = __float_as_uint(__uint_as_float(v.w) + o.w);
+                }
+                *reinterpret_cast<uint4*>(p) = v;
+              } else {
+                __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(args.D) + d_off + (long long)grow * args.ldd + col;
+                if (args.accumulate) {
+                  uint4 o = *reinterpret_cast<const uint4*>(p);
+                  float2 a0 = unpack_bf16x2(v.x), a1 = unpack_bf16x2(v.y), a2 = unpack_bf16x2(v.z), a3 = unpack_bf16x2(v.w);
+                  float2 b0 = unpack_bf16x2(o.x), b1 = unpack_bf16x2(o.y), b2 = unpack_bf16x2(o.z), b3 = unpack_bf16x2(o.w);
+                  v.x = pack_bf16x2(a0.x + b0.x, a0.y + b0.y); v.y = pack_bf16x2(a1.x + b1.x, a1.y + b1.y);
+                  v.z = pack_bf16x2(a2.x + b2.x, a2.y + b2.y); v.w = pack_bf16x2(a3.x + b3.x, a3.y + b3.y);
+                }
+                *reinterpret_cast<uint4*>(p) = v;
               }
             }
           }
@@ -401,7 +520,7 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
                         long long b_rows, long long b_cols, long long ldb, long long d_rows,
                         long long ldd, const int* offs, int num_groups, int b_group_rows,
                         long long d_group_stride, int out_fp32, int accumulate,
-                        int use_tma_store, int bn, int max_ctas, void* stream_) {
+                        int use_tma_store, int epi, int bn, int max_ctas, void* stream_) {
   using namespace pt;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -416,17 +535,28 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
   else rc = encode_tmap_2d(&tmB, B, TM_BF16, b_rows, b_cols, ldb, BK, 64, TM_SW_128);
   if (rc) return 2000 + rc;
   bool tma_store_ok = use_tma_store && !out_fp32 && !accumulate && mode != GEMM_KGROUP && (N % 8 == 0);
+  bool tma_reduce = (epi == 2) && accumulate && (N % 8 == 0);
   if (tma_store_ok) {
     rc = encode_tmap_2d(&tmD, D, TM_BF16, d_rows, N, ldd, 32, 64, TM_SW_128);
     if (rc) return 3000 + rc;
+  } else if (tma_reduce) {
+    TmDtype dt = out_fp32 ? TM_F32 : TM_BF16;
+    uint32_t box_cols = out_fp32 ? 32 : 64;
+    if (mode == GEMM_KGROUP)
+      rc = encode_tmap_3d(&tmD, D, dt, num_groups, M, N, ldd, d_group_stride, 1, 32, box_cols, TM_SW_128);
+    else
+      rc = encode_tmap_2d(&tmD, D, dt, d_rows, N, ldd, 32, box_cols, TM_SW_128);
+    if (rc) return 3000 + rc;
   } else {
     tmD = tmA;
+    if (epi == 2) epi = 1;
   }
   GemmArgs args;
   args.M = M; args.N = N; args.K = K; args.mode = mode; args.num_groups = num_groups;
   args.offs = offs; args.b_group_rows = b_group_rows; args.D = D; args.ldd = ldd;
   args.d_group_stride = d_group_stride; args.out_fp32 = out_fp32; args.accumulate = accumulate;
   args.use_tma_store = tma_store_ok ? 1 : 0;
+  args.epi = epi;
   args.err = device_status_word();
 
   int sms = sm_count();

@@ -24,6 +24,8 @@ DENSE, MGROUP, KGROUP = 0, 1, 2
 # Module-level switches used by tests and tuning runs.
 USE_TMA_STORE = True
 FORCE_BN = 0
+# accumulate epilogue: 0 = staged coalesced read-modify-write, 1 = per-thread rows, 2 = TMA reduce-add
+ACC_EPILOGUE = 2
 
 
 def _launch(a, b, d, mode, M, N, K, a_mn, b_mn, a_shape, lda, b_shape, ldb, d_rows, ldd,
@@ -35,7 +37,7 @@ def _launch(a, b, d, mode, M, N, K, a_mn, b_mn, a_shape, lda, b_shape, ldb, d_ro
         a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, M, N, K, int(a_mn), int(b_mn),
         a_shape[0], a_shape[1], lda, b_shape[0], b_shape[1], ldb, d_rows, ldd,
         None if offs is None else offs.data_ptr(), num_groups, b_group_rows, d_group_stride,
-        out_fp32, int(accumulate), int(USE_TMA_STORE), FORCE_BN, max_ctas, _native.stream_ptr(),
+        out_fp32, int(accumulate), int(USE_TMA_STORE), ACC_EPILOGUE, FORCE_BN, max_ctas, _native.stream_ptr(),
     )
     _native.check(rc, "pt_gemm_bf16")
 

@@ -53,8 +53,15 @@ def test_dense_nn(M, N, K):
     assert calc_diff(out.float(), dy.float() @ w.float()) < 1e-4
 
 
+@pytest.fixture(params=[0, 1, 2])
+def acc_epilogue(request):
+    G.ACC_EPILOGUE = request.param
+    yield request.param
+    G.ACC_EPILOGUE = 2
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (1000, 776, 328), (4096, 512, 2048)])
-def test_dense_tn(M, N, K):
+def test_dense_tn(M, N, K, acc_epilogue):
     dy, x = _rand(M, N), _rand(M, K)
     out = G.gemm_tn(dy, x, out_dtype=torch.float32)
     _native.check_status()
@@ -107,7 +114,7 @@ def test_grouped_nt_nn(sizes, N, K):
 
 @pytest.mark.parametrize("sizes", [[128, 256], [16, 0, 48, 304], [208] * 8, [1024, 16, 640, 0, 272]])
 @pytest.mark.parametrize("N,K", [(256, 128), (768, 2048), (192, 320)])
-def test_grouped_tn(sizes, N, K):
+def test_grouped_tn(sizes, N, K, acc_epilogue):
     offs = _offsets(sizes)
     R = int(offs[-1]) + 64
     Gn = len(sizes)
