@@ -243,18 +243,23 @@ class SwiGLUExperts(nn.Module):
 class MoEBlock(nn.Module):
     """Gate + local experts with the stage-1/3/5 split and expert-parallel bookkeeping."""
 
-    def __init__(self, gate: Gate, experts: nn.Module, num_experts: int, top_k: int):
+    def __init__(self, gate: Gate, experts: nn.Module, num_experts: int, top_k: int, gate_attr: str = "gate"):
         super().__init__()
+        self._gate_attr = gate_attr
         self.num_experts, self.num_experts_per_tok = num_experts, top_k
         self.ep_size, self.ep_rank = distributed.ep_size, distributed.ep_rank
         assert num_experts % self.ep_size == 0
         self.experts_per_rank = num_experts // self.ep_size
-        self.gate = gate
+        setattr(self, gate_attr, gate)
         self.experts = experts
+
+    @property
+    def router_module(self) -> Gate:
+        return getattr(self, self._gate_attr)
 
     # stage 1 tail
     def route(self, tokens: torch.Tensor) -> RoutingInfo:
-        idx, w, lb_loss = self.gate(tokens)
+        idx, w, lb_loss = self.router_module(tokens)
         if lb_loss is not None:
             MoELoadBalanceLossTracker.add(lb_loss)
         plan = None
@@ -279,7 +284,7 @@ class MoEBlock(nn.Module):
 
     def reference_forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """Single-rank oracle (all experts local)."""
-        idx, w, lb_loss = self.gate(tokens, reference=True)
+        idx, w, lb_loss = self.router_module(tokens, reference=True)
         if lb_loss is not None:
             MoELoadBalanceLossTracker.add(lb_loss)
         return self.experts.reference(tokens, w, idx)
