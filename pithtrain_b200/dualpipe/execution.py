@@ -183,6 +183,19 @@ class _CommRegion:
             self.ctx.comp_stream.wait_event(self.event)
             self.event = None
 
+    def share(self, produced=(), consumed=()) -> None:
+        """Tell the caching allocator about cross-stream use: ``produced`` tensors were allocated on the
+        communication stream and will be read on the compute stream, ``consumed`` the other way."""
+        c = self.ctx
+        if c.comm_stream is None:
+            return
+        for t in produced:
+            if t is not None and t.is_cuda:
+                t.record_stream(c.comp_stream)
+        for t in consumed:
+            if t is not None and t.is_cuda:
+                t.record_stream(c.comm_stream)
+
 
 def _ep():
     from ..parallel import ep as _ep_mod
@@ -222,6 +235,7 @@ def stage2_f(ctx: ExecutionCtx, layer, rec: LayerRecord, tokens, routing):
         with region:
             recv_x, recv_w = ep.dispatch(x, w, routing.plan)
             rec.s2.end(recv_x, recv_w)
+        region.share(produced=(recv_x, recv_w), consumed=(x, w))
     return region
 
 
@@ -230,6 +244,7 @@ def stage2_b(ctx: ExecutionCtx, layer, rec: LayerRecord, grads):
         region = ctx.comm()
         with region:
             out = rec.s2.backward(grads)
+        region.share(produced=out, consumed=grads)
     return out, region
 
 
@@ -269,6 +284,7 @@ def stage4_f(ctx: ExecutionCtx, layer, rec: LayerRecord, outs, routing):
         with region:
             back = ep.combine(p, routing.plan)
             rec.s4.end(back)
+        region.share(produced=(back,), consumed=(p,))
     return region
 
 
@@ -277,6 +293,7 @@ def stage4_b(ctx: ExecutionCtx, layer, rec: LayerRecord, grads):
         region = ctx.comm()
         with region:
             out = rec.s4.backward(grads)
+        region.share(produced=out, consumed=grads)
     return out, region
 
 

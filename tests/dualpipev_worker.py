@@ -18,6 +18,10 @@ CONFIGS = {
                   rms_norm_eps=1e-6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
                   norm_topk_prob=True, vocab_size=96, num_hidden_layers=4, max_position_embeddings=64, rope_theta=1e6,
                   attention_bias=False),
+    "qwen3_gpu": dict(model_type="qwen3_moe", hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                      rms_norm_eps=1e-6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                      norm_topk_prob=True, vocab_size=512, num_hidden_layers=4, max_position_embeddings=128,
+                      rope_theta=1e6, attention_bias=False),
     "deepseek": dict(model_type="deepseek_v2", hidden_size=64, num_attention_heads=4, qk_rope_head_dim=8,
                      qk_nope_head_dim=16, kv_lora_rank=32, v_head_dim=16, q_lora_rank=None, rms_norm_eps=1e-6,
                      n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, n_shared_experts=2,
@@ -53,7 +57,7 @@ def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int
     dev = distributed.device
     mc = SimpleNamespace(**CONFIGS[model_key])
     Model = MODEL_CLASSES[mc.model_type]
-    V, S, B = mc.vocab_size, 16, 1
+    V, S, B = mc.vocab_size, (16 if device_type == "cpu" else 128), 1
     dtype = torch.float32 if device_type == "cpu" else torch.bfloat16
     dp_like = ep  # every ep rank reads its own micro-batches
 
