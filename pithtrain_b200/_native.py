@@ -64,6 +64,7 @@ SIGS = {
     "pt_router_topk_fwd": "PIPPPIIIIIFP",
     "pt_router_topk_bwd": "PPPPPPIIIIIIFP",
     "pt_route_sort": "PPIIIPPPPIP",
+    "pt_route_sort_noalloc": "PIIIPPPIP",
     "pt_gather_rows": "PPIPPIILP",
     "pt_combine": "PPPPPPIIIP",
     "pt_swiglu_fwd": "PPPIIIFFP",

@@ -10,7 +10,10 @@
 // (pithtrain/operators/token_scatter.py:38-153, pithtrain/models/qwen3_moe.py:81-89,229-245,
 // pithtrain/operators/silu_mul.py:28-87, pithtrain/operators/clamped_swiglu.py:18-89).
 #include "elementwise.cuh"
+#include <mutex>
+
 #include "host_common.h"
+#include "no_alloc.h"
 #include "ptx.cuh"
 
 namespace pt {
@@ -480,6 +483,62 @@ PT_API int pt_route_sort(const int* eids, const int* n_ptr, int n_max, int E, in
                                                   row_of_slot, slot_of_row, r_cap, device_status_word());
   int m = n_max > r_cap ? n_max : r_cap;
   route_fill_kernel<<<(m + 255) / 256, 256, 0, st>>>(eids, n_ptr, n_max, E, offs, row_of_slot, slot_of_row, r_cap);
+  return (int)cudaGetLastError();
+}
+
+// ----------------------------------------------------------------------------------------------
+// Routing sort for callers that must not allocate (declaration and contract: no_alloc.h).
+// ----------------------------------------------------------------------------------------------
+// Per-expert counters of the no-allocation variant. In host code this name is only a handle for
+// the runtime, not a device address: the address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) int g_route_counts_scratch[PT_ROUTE_SORT_NOALLOC_MAX_EXPERTS];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+int* g_route_counts_addr[kNoAllocMaxDevices] = {nullptr};
+std::mutex g_route_counts_mu;
+
+// Device address of the scratch on the current device; resolved once per device.
+int route_counts_scratch(int** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return -1;
+  std::lock_guard<std::mutex> lk(g_route_counts_mu);
+  if (!g_route_counts_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_route_counts_scratch);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[pithtrain_b200] cudaGetSymbolAddress(route counters) failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return (int)e;
+    }
+    g_route_counts_addr[dev] = static_cast<int*>(p);
+  }
+  *out = g_route_counts_addr[dev];
+  return 0;
+}
+}  // namespace
+
+PT_API int pt_route_sort_noalloc(const int* eids, int n, int E, int align, int* offs, int* row_of_slot,
+                                 int* slot_of_row, int r_cap, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (E <= 0 || n < 0 || align <= 0 || r_cap < 0 || !eids || !offs || !row_of_slot || !slot_of_row) return -1;
+  if (E > PT_ROUTE_SORT_NOALLOC_MAX_EXPERTS) {
+    fprintf(stderr, "[pithtrain_b200] pt_route_sort_noalloc: %d experts exceed the static scratch (max %d)\n", E,
+            PT_ROUTE_SORT_NOALLOC_MAX_EXPERTS);
+    return -2;
+  }
+  int* counts = nullptr;
+  int rc = route_counts_scratch(&counts);
+  if (rc != 0) return rc;
+  // every counter in [0, E) is overwritten by the count kernel, nothing has to be cleared first
+  route_count_kernel<<<E, ROUTE_THREADS, 0, st>>>(eids, nullptr, n, E, counts);
+  route_place_kernel<<<E, ROUTE_THREADS, 0, st>>>(eids, nullptr, n, E, align, counts, offs, row_of_slot,
+                                                  slot_of_row, r_cap, nullptr);
+  int m = n > r_cap ? n : r_cap;
+  if (m > 0)
+    route_fill_kernel<<<(m + 255) / 256, 256, 0, st>>>(eids, nullptr, n, E, offs, row_of_slot, slot_of_row, r_cap);
   return (int)cudaGetLastError();
 }
 
