@@ -132,13 +132,20 @@ class Muon(torch.optim.Optimizer):
                     self._unit_state[key] = st
                     sv = st.view(E, 2, I, H)
                     for i, q in enumerate(fw.params):
+                        prev = self.state[q].get("momentum_buffer")
+                        if prev is not None:  # restored from a checkpoint before the first step
+                            sv[:, i].copy_(prev)
                         self.state[q]["momentum_buffer"] = sv[:, i]
                 units.append(_Unit(w, gg, list(fw.params), key))
             else:
                 key = id(p)
                 if key not in self._unit_state:
                     if "momentum_buffer" in self.state[p]:  # restored from a checkpoint
-                        self._unit_state[key] = self.state[p]["momentum_buffer"]
+                        prev = self.state[p]["momentum_buffer"]
+                        st = self._new_state(p)
+                        st.copy_(prev)
+                        self._unit_state[key] = st
+                        self.state[p]["momentum_buffer"] = st
                     else:
                         self._unit_state[key] = self._new_state(p)
                         self.state[p]["momentum_buffer"] = self._unit_state[key]
