@@ -75,6 +75,20 @@ SIGS = {
     "pt_sumsq": "PILPP",
     "pt_adamw": "PIPIPPLPFFFFFFFP",
     "pt_muon_momentum": "PIPIPLFP",
+    "pt_symm_malloc": "PL",
+    "pt_symm_free": "P",
+    "pt_ipc_export": "PP",
+    "pt_ipc_import": "PP",
+    "pt_ipc_close": "P",
+    "pt_ipc_handle_size": "",
+    "pt_can_access_peer": "II",
+    "pt_ep_chan_struct_size": "",
+    "pt_ep_plan": "PIIIIIPPPPP",
+    "pt_ep_push": "PIIPLPPPPPP",
+    "pt_ep_receive": "PIIPPPPIP",
+    "pt_ep_return": "PIIPPPPP",
+    "pt_ep_wait_returned": "PIIP",
+    "pt_ep_ack": "PIIP",
     "pt_axpby_bf16": "PPLFFP",
 }
 

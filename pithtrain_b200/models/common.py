@@ -278,7 +278,7 @@ class MoEBlock(nn.Module):
 
     # stage 5 head
     def finish(self, outs: torch.Tensor, routing: RoutingInfo) -> torch.Tensor:
-        if routing.plan is None:
+        if routing.plan is None or getattr(routing.plan, "reduced", False):
             return outs
         return ep_mod.home_reduce(outs, routing.plan)
 

@@ -43,7 +43,7 @@ def _canonical(name: str) -> str:
 
 
 def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int, overlap: bool = True,
-        device_type: str = "cpu"):
+        device_type: str = "cpu", ep_backend: str = "nccl"):
     from pithtrain_b200.contexts import distributed
     from pithtrain_b200.dualpipe.dualpipev import DualPipeV
     from pithtrain_b200.dualpipe.comm import set_p2p_tensor_dtype, set_p2p_tensor_shapes
@@ -93,7 +93,7 @@ def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int
 
     # ---- distributed: slice by stage and expert rank
     distributed.ep_size, distributed.ep_rank, distributed.pp_size, distributed.pp_rank = ep_saved
-    ep_mod.setup_exchange("nccl")
+    ep_mod.setup_exchange(ep_backend)
     torch.set_default_dtype(dtype)
     with torch.device(dev):
         chunks = [Model(mc, 0), Model(mc, 1)]

@@ -22,3 +22,21 @@ def test_qwen3_two_gpus(pp, ep):
 def test_qwen3_pp2_ep2_four_gpus():
     _need(4)
     launch(4, dualpipev_worker.run, "qwen3_gpu", 2, 2, 5, True, "cuda", backend="nccl")
+
+
+@pytest.mark.parametrize("m,H,E,k", [(256, 512, 8, 2), (1000, 256, 16, 4)])
+def test_fused_exchange_matches_all_to_all(m, H, E, k):
+    _need(2)
+    import ep_fused_worker
+
+    launch(2, ep_fused_worker.run, m, H, E, k, backend="nccl")
+
+
+def test_qwen3_ep2_fused_transport():
+    _need(2)
+    launch(2, dualpipev_worker.run, "qwen3_gpu", 1, 2, 3, True, "cuda", "fused", backend="nccl")
+
+
+def test_qwen3_pp2_ep2_fused_transport_four_gpus():
+    _need(4)
+    launch(4, dualpipev_worker.run, "qwen3_gpu", 2, 2, 5, True, "cuda", "fused", backend="nccl")
