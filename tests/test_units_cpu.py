@@ -1,0 +1,282 @@
+"""CPU unit tests of the framework's pure logic: schedule, partitioning, optimizers, configs, data,
+load-balance losses, MoE index math, native signature table."""
+import glob
+import math
+import re
+from dataclasses import dataclass
+from datetime import timedelta
+from functools import partial
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+# ------------------------------------------------------------------------------------------------ schedule
+@pytest.mark.parametrize("P", [1, 2, 3, 4, 8])
+def test_schedule_simulation(P):
+    from pithtrain_b200.dualpipe.schedule import build_schedule, simulate
+
+    for N in (2 * P, 2 * P + 1, 3 * P + 2, 4 * P):
+        simulate(P, N)
+        for r in range(P):
+            acts = build_schedule(P, r, N)
+            f = sum(a.kind in ("F", "FB") for a in acts)
+            assert f == 2 * N  # every micro-batch passes both local chunks
+    with pytest.raises(AssertionError):
+        build_schedule(P, 0, 2 * P - 1)
+
+
+def test_layer_partition_properties():
+    from pithtrain_b200.dualpipe.dualpipev import layer_partition
+
+    for L in range(1, 70):
+        for S in (1, 2, 4, 6, 8, 16):
+            parts = [layer_partition(L, S, i) for i in range(S)]
+            flat = [x for p in parts for x in p]
+            assert flat == list(range(L))
+            sizes = [len(p) for p in parts]
+            assert max(sizes) - min(sizes) <= 1
+            if S > 2 and L % S and L % S <= S - 2:
+                assert sizes[0] == min(sizes) and sizes[-1] == min(sizes)  # edges stay light
+    assert [len(layer_partition(27, 4, i)) for i in range(4)] == [7, 7, 7, 6]
+
+
+# ------------------------------------------------------------------------------------------------ config
+def test_slotted_default_and_json():
+    from pithtrain_b200.config import SlottedDefault
+
+    @dataclass(init=False, slots=True)
+    class Cfg(SlottedDefault):
+        need: int
+        opt: int = 3
+        path: Path = Path("/x")
+        t: timedelta = timedelta(minutes=1)
+        fn: object = None
+
+    c = Cfg()
+    assert c.opt == 3 and not hasattr(c, "need")
+    c.fn = partial(math.pow, y=2)
+    j = c.to_json_dict()
+    assert j["path"] == "/x" and j["t"] == 60.0 and j["fn"] == "pow(y=2)" and "need" not in j
+
+
+def test_wsd_schedule():
+    from pithtrain_b200.modules.training import wsd_lambda
+
+    fn = wsd_lambda(100, 1.0, start_lr=0.0, warmup_ratio=0.1, final_lr=0.1, decay_ratio=0.2, decay_shape="linear")
+    assert fn(0) == 0.0 and abs(fn(5) - 0.5) < 1e-9 and fn(10) == 1.0 and fn(79) == 1.0
+    assert abs(fn(90) - 0.55) < 1e-9 and abs(fn(100) - 0.1) < 1e-9
+    cos = wsd_lambda(100, 1.0, decay_ratio=0.5, decay_shape="cosine")
+    assert abs(cos(75) - 0.5) < 1e-9
+    with pytest.raises(ValueError):
+        wsd_lambda(10, 1.0, warmup_ratio=0.6, decay_ratio=0.6)
+
+
+# ------------------------------------------------------------------------------------------------ optimizers
+def test_is_muon_param_table():
+    from pithtrain_b200.modules.training import is_muon_param
+
+    m2, m3, m1 = torch.zeros(4, 4), torch.zeros(2, 4, 4), torch.zeros(4)
+    yes = ["layers.0.self_attn.q_proj.weight", "layers.0.self_attn.kv_b_proj.weight", "layers.1.mlp.gate_proj.weight",
+           "layers.1.mlp.shared_experts.down_proj.weight"]
+    for n in yes:
+        assert is_muon_param(n, m2), n
+    assert is_muon_param("layers.1.mlp.experts.gate_proj.weight", m3)
+    assert is_muon_param("layers.1.mlp.experts.gate_up_proj", m3)
+    no = [("layers.0.input_layernorm.weight", m1), ("layers.0.self_attn.q_proj.bias", m1),
+          ("layers.0.mlp.experts.gate_up_proj_bias", m2), ("embed_tokens.weight", m2), ("lm_head.weight", m2),
+          ("layers.0.mlp.gate.weight", m2), ("layers.0.mlp.router.weight", m2), ("layers.0.self_attn.sinks", m1)]
+    for n, t in no:
+        assert not is_muon_param(n, t), n
+
+
+@pytest.mark.parametrize("shape", [(16, 64), (64, 16), (3, 24, 40)])
+def test_newton_schulz_orthogonalises(shape):
+    from pithtrain_b200.modules.optimizer import muon_scale_factor, zeropower_via_newtonschulz5
+
+    torch.manual_seed(0)
+    G = torch.randn(*shape)
+    X = zeropower_via_newtonschulz5(G, steps=5).float()
+    sv = torch.linalg.svdvals(X)
+    assert float(sv.min()) > 0.5 and float(sv.max()) < 1.5
+    U, _, Vh = torch.linalg.svd(G, full_matrices=False)
+    cos = (X * (U @ Vh)).sum() / (X.norm() * (U @ Vh).norm())
+    assert float(cos) > 0.97
+    assert muon_scale_factor(16, 64) == 0.2 * 8.0
+
+
+def test_muon_step_matches_formula():
+    from pithtrain_b200.modules.optimizer import Muon, muon_scale_factor, zeropower_via_newtonschulz5
+
+    torch.manual_seed(1)
+    p = torch.nn.Parameter(torch.randn(8, 12))
+    g1, g2 = torch.randn(8, 12), torch.randn(8, 12)
+    opt = Muon([p], lr=0.1, momentum=0.9, weight_decay=0.05)
+    w, buf = p.detach().clone(), torch.zeros(8, 12)
+    for g in (g1, g2):
+        p.grad = g.clone()
+        opt.step()
+        buf = buf.lerp(g, 0.1)
+        upd = g.lerp(buf, 0.9)
+        o = zeropower_via_newtonschulz5(upd).float() * muon_scale_factor(8, 12)
+        w = w * (1 - 0.1 * 0.05) - 0.1 * o
+    assert torch.allclose(p.detach(), w, atol=1e-5)
+    p.grad = g1.bfloat16().float()
+    opt.step()  # bf16-rounded gradients are fine
+
+
+def test_adamw_matches_torch():
+    from pithtrain_b200.modules.optimizer import AdamW
+
+    torch.manual_seed(2)
+    a = torch.nn.Parameter(torch.randn(5, 7))
+    b = torch.nn.Parameter(a.detach().clone())
+    mine, ref = AdamW([a], lr=1e-2, weight_decay=0.1), torch.optim.AdamW([b], lr=1e-2, weight_decay=0.1)
+    for _ in range(3):
+        g = torch.randn(5, 7)
+        a.grad, b.grad = g.clone(), g.clone()
+        mine.step(); ref.step()
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------------ load balance
+def test_load_balance_losses():
+    from pithtrain_b200.modules.load_balance import (MoELoadBalanceLossInjector, SequenceLevelLoadBalanceLoss,
+                                                     force_balance, make_load_balance_loss_fn)
+
+    torch.manual_seed(0)
+    n, E, k = 64, 8, 2
+    scores = torch.rand(n, E).softmax(-1).requires_grad_()
+    idx = torch.topk(scores, k).indices
+    fn = make_load_balance_loss_fn("micro-batch", 0.5)
+    f = torch.bincount(idx.flatten(), minlength=E).float() / (n * k)
+    assert torch.allclose(fn(scores, idx, E, k), 0.5 * E * (f * scores.mean(0)).sum())
+    bal = force_balance(E)(idx)
+    assert torch.bincount(bal.flatten(), minlength=E).tolist() == [n * k // E] * E
+    g = make_load_balance_loss_fn("global-batch", 1.0)
+    l1 = g(scores, bal, E, k)
+    assert abs(float(l1) - 1.0) < 1e-5  # perfectly balanced counts: E * sum(1/E * mean prob) = 1
+    g.reset()
+    s = SequenceLevelLoadBalanceLoss(1.0, 32)
+    assert s(scores, idx, E, k).ndim == 0
+    w = torch.ones(3, requires_grad=True)
+    lb = (scores.sum() * 0 + scores[0, 0]) * 2
+    out = MoELoadBalanceLossInjector.apply(w, lb)
+    out.sum().backward()
+    assert scores.grad[0, 0] == 2.0 and torch.equal(w.grad, torch.ones(3))
+
+
+# ------------------------------------------------------------------------------------------------ MoE index math
+def test_route_sort_ref_invariants():
+    from pithtrain_b200.ops.moe import ALIGN, route_sort, sorted_capacity
+
+    torch.manual_seed(0)
+    n, k, E = 50, 3, 7
+    eids = torch.randint(-1, E, (n, k), dtype=torch.int32)
+    offs, ros, sor = route_sort(eids, E)
+    assert sor.numel() == sorted_capacity(n * k, E)
+    flat = eids.flatten()
+    for e in range(E):
+        a, b = int(offs[e]), int(offs[e + 1])
+        assert (b - a) % ALIGN == 0
+        slots = sor[a:b][sor[a:b] >= 0]
+        assert torch.equal(flat[slots.long()], torch.full_like(slots, e))
+        assert torch.equal(slots, slots.sort().values)  # stable: slot order inside a group
+        assert slots.numel() == int((flat == e).sum())
+    assert bool((ros[flat < 0] == -1).all())
+    valid = flat >= 0
+    assert torch.equal(sor[ros[valid].long()].long(), torch.nonzero(valid).flatten())
+
+
+def test_ep_send_plan_index_math():
+    from pithtrain_b200.parallel.ep import build_send_side
+
+    torch.manual_seed(0)
+    m, k, E, ep = 40, 4, 16, 4
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(m)]).int()
+    tok, pos, eids, counts = build_send_side(idx, E, ep)
+    epr = E // ep
+    dest = idx.long() // epr
+    assert counts.tolist() == [int((dest == g).any(1).sum()) for g in range(ep)]
+    assert tok.numel() == int(counts.sum())
+    for t in range(m):
+        for g in range(ep):
+            p = int(pos[t, g])
+            if (dest[t] == g).any():
+                assert int(tok[p]) == t
+                row = eids[p]
+                want = torch.where(dest[t] == g, idx[t].long() - g * epr, torch.full((k,), -1)).int()
+                assert torch.equal(row, want)
+            else:
+                assert p == -1
+    # expected de-duplicated volume under uniform routing
+    exp = m * (1 - ((ep - 1) / ep) ** k)
+    assert abs(float(counts.float().mean()) - exp) < 0.35 * exp
+
+
+def test_moe_experts_cpu_vs_loop():
+    from pithtrain_b200.ops import moe as M
+
+    torch.manual_seed(0)
+    n, k, E, H, I = 33, 2, 4, 16, 8
+    x, w = torch.randn(n, H, requires_grad=True), torch.rand(n, k, requires_grad=True)
+    eids = torch.stack([torch.randperm(E)[:k] for _ in range(n)]).int()
+    eids[::5, 1] = -1
+    w1, w2 = torch.randn(E, 2 * I, H) * 0.2, torch.randn(E, H, I) * 0.2
+    b1, b2 = torch.nn.Parameter(torch.randn(E, 2 * I) * 0.1), torch.nn.Parameter(torch.randn(E, H) * 0.1)
+    g1, g2 = torch.zeros_like(w1), torch.zeros_like(w2)
+    for inter, limit in ((False, 0.0), (True, 7.0)):
+        ew = M.ExpertWeights(w1, w2, lambda: g1, lambda: g2, b1=b1, b2=b2, interleaved=inter, alpha=1.702 if inter else 1.0, limit=limit)
+        g1.zero_(); g2.zero_(); b1.grad = None; b2.grad = None
+        x.grad = None; w.grad = None
+        out = M.moe_experts(x, w, eids, ew)
+        go = torch.randn(n, H)
+        out.backward(go)
+        got = (out.detach(), x.grad.clone(), w.grad.clone(), g1.clone(), g2.clone(), b1.grad.clone(), b2.grad.clone())
+        leaves = [t.detach().clone().requires_grad_() for t in (x, w, w1, w2, b1, b2)]
+        ref = M.moe_experts_ref(leaves[0], leaves[1], eids, leaves[2], leaves[3], leaves[4], leaves[5], inter, 1.702 if inter else 1.0, limit)
+        ref.backward(go)
+        want = (ref.detach(), leaves[0].grad, leaves[1].grad, leaves[2].grad, leaves[3].grad, leaves[4].grad, leaves[5].grad)
+        for a, b in zip(got, want):
+            assert torch.allclose(a, b, atol=1e-4, rtol=1e-4)
+
+
+# ------------------------------------------------------------------------------------------------ data
+def test_datasets(tmp_path):
+    from pithtrain_b200.modules.dataset import ConcatDataset, MemmapDataset, SyntheticDataset
+
+    for i, n in enumerate((41, 25)):
+        with open(tmp_path / f"s{i}.bin", "wb") as f:
+            np.save(f, (np.arange(n) + 100 * i).astype(np.uint16))
+    a = MemmapDataset(tmp_path / "s0.bin", 8)
+    assert len(a) == 5
+    t, l = a[1]
+    assert t.tolist() == list(range(8, 16)) and l.tolist() == list(range(9, 17))
+    t, l = a.get_chunk(1, 2, 3)
+    assert t.tolist() == [10, 11, 12] and l.tolist() == [11, 12, 13]
+    c = ConcatDataset([a, MemmapDataset(tmp_path / "s1.bin", 8)], seed=3)
+    assert len(c) == 8
+    seen = sorted(int(c[i][0][0]) for i in range(8))
+    assert seen == [0, 8, 16, 24, 32, 100, 108, 116]
+    s = SyntheticDataset(1000, 16, seed=5)
+    assert torch.equal(s[7][0], s[7][0]) and not torch.equal(s[7][0], s[8][0])
+    assert torch.equal(s.get_chunk(7, 4, 4)[0], s[7][0][4:8]) and int(s[3][0].max()) < 1000
+
+
+# ------------------------------------------------------------------------------------------------ native ABI table
+def test_native_signature_table_matches_sources():
+    from pithtrain_b200._native import SIGS
+
+    src = "".join(open(f).read() for f in glob.glob(str(ROOT / "pithtrain_b200" / "csrc" / "*.cu")))
+    found = 0
+    for m in re.finditer(r"PT_API int (\w+)\(([^)]*)\)", src):
+        name, args = m.group(1), [a.strip() for a in m.group(2).split(",") if a.strip()]
+        sig = "".join("P" if "*" in a else "L" if a.startswith("long long") else "F" if a.startswith("float") else "I" for a in args)
+        assert name in SIGS, f"{name} is exported but has no ctypes signature"
+        assert SIGS[name] == sig, (name, SIGS[name], sig)
+        found += 1
+    assert found >= 30
