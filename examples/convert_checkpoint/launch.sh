@@ -1,0 +1,9 @@
+#!/bin/bash
+# Run one checkpoint conversion example:  bash examples/convert_checkpoint/launch.sh <example directory name> [extra args]
+set -euo pipefail
+[ $# -ge 1 ] || { echo "usage: $0 <example directory name> [args]" >&2; exit 2; }
+export PYTHONUNBUFFERED=1
+NAME=$1; shift
+LOG=logging/convert_checkpoint/${NAME}_node${SLURM_NODEID:-0}.log
+mkdir -p "$(dirname "$LOG")"
+python "examples/convert_checkpoint/$NAME/script.py" "$@" 2>&1 | tee "$LOG"

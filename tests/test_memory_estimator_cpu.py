@@ -1,0 +1,62 @@
+"""Memory estimator: parameter counts against the real modules (meta device), schedule accounting, CLI."""
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from pithtrain_b200.tools.memory_estimator import ModelDims, ParallelCfg, estimate, static_memory
+from pithtrain_b200.tools.memory_estimator.__main__ import main
+
+ROOT = Path(__file__).resolve().parents[1]
+CONFIGS = sorted((ROOT / "examples" / "pretrain_lm").glob("*/config.json"))
+
+
+@pytest.mark.parametrize("path", CONFIGS, ids=lambda p: p.parent.name)
+def test_parameter_count_matches_meta_model(path):
+    from pithtrain_b200.modules.training import load_model_config, model_class_for
+
+    config = load_model_config(path)
+    config.num_hidden_layers = min(config.num_hidden_layers, 4)
+    if getattr(config, "layer_types", None):
+        config.layer_types = config.layer_types[:4]
+    config.max_position_embeddings = 128
+    raw = json.load(open(path))
+    raw = raw.get("text_config", raw)
+    raw["num_hidden_layers"] = config.num_hidden_layers
+    if raw.get("layer_types"):
+        raw["layer_types"] = raw["layer_types"][:4]
+    dims = ModelDims.from_config(raw)
+    with torch.device("meta"):
+        model = model_class_for(config)(config, phase=-1)
+    actual = sum(p.numel() for p in model.parameters())
+    sm = static_memory(dims, ParallelCfg(), 0)
+    predicted = sm.params // 2
+    assert abs(predicted - actual) / actual < 2e-3, (predicted, actual)
+
+
+def test_schedule_accounting_and_scaling():
+    dims = ModelDims.from_json(ROOT / "examples/pretrain_lm/qwen3-30b-a3b/config.json")
+    one = estimate(dims, ParallelCfg(global_batch_size=32, offload_optimizer_state=True), 0)
+    # one GPU holds all parameters twice (bf16 weights + bf16 gradient accumulators)
+    assert abs(one.static.params / 2 - 30.53e9) / 30.53e9 < 0.01
+    assert 125 < one.peak_total / 2 ** 30 < 150  # measured on a B200: 142.1 GB allocated (132.4 GiB)
+    ep8 = estimate(dims, ParallelCfg(ep=8, global_batch_size=256), 0)
+    assert ep8.static.params < one.static.params / 5
+    assert ep8.comm_buffers > 0 and ep8.tokens.recv > ep8.tokens.T
+    pp = [estimate(dims, ParallelCfg(pp=4, ep=2, global_batch_size=64), r, keep_timeline=True) for r in range(4)]
+    # the first pipeline rank keeps the most forward micro-batches alive
+    assert pp[0].max_inflight[0] >= pp[3].max_inflight[0]
+    assert all(e.timeline and e.peak_total >= e.static.device_total for e in pp)
+    fp32 = estimate(dims, ParallelCfg(ep=8, global_batch_size=256, grad_dtype="fp32"), 0)
+    assert fp32.static.grads == 2 * ep8.static.grads
+
+
+def test_cli(capsys):
+    rc = main(["--model", str(ROOT / "examples/pretrain_lm/qwen3-30b-a3b/config.json"), "--pp-size", "2", "--ep-size", "4",
+               "--global-batch-size", "256", "--detail", "--timeline", "--timeline-limit", "5"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "estimated peak" in out and "per pp rank" in out and "experts.gate_up" in out
+    rc = main(["--model", str(ROOT / "examples/pretrain_lm/qwen3-30b-a3b/config.json"), "--gpu-memory-gb", "80", "--grad-dtype", "fp32"])
+    out = capsys.readouterr().out
+    assert rc == 1 and "OOM" in out and "ways to lower the peak" in out
