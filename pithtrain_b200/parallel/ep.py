@@ -177,6 +177,29 @@ class CollectiveExchange(Exchange):
         return _A2A.apply(partial, plan.recv_counts, plan.send_counts, self.group)
 
 
+def _fused_transport_usable(d) -> bool:
+    """True when every rank of the expert group sits on this node with peer access to the others.
+
+    The expert axis is the innermost mesh axis, so a group is ``ep_size`` consecutive ranks; it stays
+    inside a node when the node's rank count is a multiple of ``ep_size``. The ranks vote (MIN over the
+    group) so that all of them pick the same transport.
+    """
+    if torch.device(d.device).type != "cuda":
+        return False
+    local_world = max(int(getattr(d, "local_world_size", 1) or 1), 1)
+    ok = d.ep_size <= local_world and local_world % d.ep_size == 0
+    if ok:
+        from .. import _native
+
+        me = torch.device(d.device).index or 0
+        base = me - d.ep_rank
+        L = _native.lib()
+        ok = all(L.pt_can_access_peer(me, base + r) == 1 for r in range(d.ep_size) if base + r != me)
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=d.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=d.ep_group)
+    return bool(flag.item())
+
+
 def setup_exchange(backend: str = "auto"):
     """Create the process-wide exchange from the distributed context (call after setup_distributed)."""
     from ..contexts import distributed
@@ -185,7 +208,7 @@ def setup_exchange(backend: str = "auto"):
         set_current(None)
         return None
     if backend == "auto":
-        backend = "nccl"
+        backend = "fused" if _fused_transport_usable(distributed) else "nccl"
     if backend == "fused":
         from .ep_fused import FusedExchange
 

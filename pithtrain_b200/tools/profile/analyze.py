@@ -1,0 +1,159 @@
+"""Turn step traces into tables: per-stream busy time, compute/communication overlap, kernel classes, top kernels.
+
+    python -m pithtrain_b200.tools.profile.analyze workspace/profiles/qwen3 [--top 25] [--json out.json]
+
+Input: the ``trace_rank<r>.json[.gz]`` files written by ``capture`` (Chrome trace events; GPU work is every
+complete event of category ``kernel``, ``gpu_memcpy`` or ``gpu_memset`` and carries its stream id in ``args``).
+Per rank the tool reports
+
+* the step window (first GPU event to last) and the time no stream was busy (launch- or host-bound gaps);
+* busy time per stream (union of its intervals) — the compute stream, the communication stream, copy streams;
+* for each kernel class (gemm, attention, communication, optimizer, memcpy, other) the summed duration,
+  and for communication the share that ran while a compute kernel was running on another stream — the
+  quantity the reference's nsys analysis calls overlap
+  (.agents/skills/analyze-nsys-profile/scripts of the reference);
+* the kernels with the largest total time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import gzip
+import json
+import re
+import sys
+from collections import defaultdict
+from pathlib import Path
+from typing import Dict, Iterable, List, Tuple
+
+GPU_CATS = {"kernel", "gpu_memcpy", "gpu_memset"}
+CLASSES = [
+    ("communication", re.compile(r"nccl|pt_ep_|ep_push|ep_return|ep_receive|ep_wait|ep_ack|ep_plan|symm", re.I)),
+    ("attention", re.compile(r"fmha|flash|sdpa|attn|cudnn", re.I)),
+    ("gemm", re.compile(r"gemm|nvjet|cutlass|cublas|xmma|tcgen05", re.I)),
+    ("optimizer", re.compile(r"muon|adamw|sumsq|axpby|newton", re.I)),
+]
+Interval = Tuple[float, float]
+
+
+def classify(name: str, cat: str) -> str:
+    if cat != "kernel":
+        return "memcpy"
+    for label, rx in CLASSES:
+        if rx.search(name):
+            return label
+    return "other"
+
+
+def load_events(path: Path) -> List[dict]:
+    opener = gzip.open if path.suffix == ".gz" else open
+    with opener(path, "rt") as f:
+        data = json.load(f)
+    events = data["traceEvents"] if isinstance(data, dict) else data
+    out = []
+    for e in events:
+        if e.get("ph") == "X" and e.get("cat") in GPU_CATS and e.get("dur") is not None:
+            out.append({"name": e.get("name", "?"), "cat": e["cat"], "ts": float(e["ts"]), "dur": float(e["dur"]),
+                        "stream": (e.get("args") or {}).get("stream", e.get("tid", 0))})
+    return out
+
+
+def union(intervals: Iterable[Interval]) -> List[Interval]:
+    merged: List[Interval] = []
+    for s, e in sorted(intervals):
+        if merged and s <= merged[-1][1]:
+            if e > merged[-1][1]:
+                merged[-1] = (merged[-1][0], e)
+        else:
+            merged.append((s, e))
+    return merged
+
+
+def total(intervals: Iterable[Interval]) -> float:
+    return sum(e - s for s, e in intervals)
+
+
+def intersect(a: List[Interval], b: List[Interval]) -> float:
+    """Summed length of the intersection of two merged interval lists."""
+    i = j = 0
+    acc = 0.0
+    while i < len(a) and j < len(b):
+        lo, hi = max(a[i][0], b[j][0]), min(a[i][1], b[j][1])
+        if hi > lo:
+            acc += hi - lo
+        if a[i][1] < b[j][1]:
+            i += 1
+        else:
+            j += 1
+    return acc
+
+
+def analyze_events(events: List[dict], top: int = 25) -> Dict:
+    if not events:
+        return {"window_us": 0.0, "streams": {}, "classes": {}, "top": [], "idle_us": 0.0, "comm_overlap": None}
+    t0 = min(e["ts"] for e in events)
+    t1 = max(e["ts"] + e["dur"] for e in events)
+    by_stream: Dict[str, List[Interval]] = defaultdict(list)
+    by_class: Dict[str, List[dict]] = defaultdict(list)
+    by_name: Dict[str, List[float]] = defaultdict(list)
+    for e in events:
+        iv = (e["ts"], e["ts"] + e["dur"])
+        by_stream[str(e["stream"])].append(iv)
+        c = classify(e["name"], e["cat"])
+        e["cls"] = c
+        by_class[c].append(e)
+        by_name[e["name"]].append(e["dur"])
+    busy_all = union((e["ts"], e["ts"] + e["dur"]) for e in events)
+    streams = {s: {"busy_us": total(union(iv)), "launches": len(iv)} for s, iv in by_stream.items()}
+    comm = union((e["ts"], e["ts"] + e["dur"]) for e in by_class.get("communication", []))
+    comm_streams = {str(e["stream"]) for e in by_class.get("communication", [])}
+    compute = union((e["ts"], e["ts"] + e["dur"]) for e in events
+                    if e["cls"] in ("gemm", "attention", "other", "optimizer") and str(e["stream"]) not in comm_streams)
+    classes = {c: {"sum_us": sum(e["dur"] for e in evs), "launches": len(evs)} for c, evs in by_class.items()}
+    overlap = (intersect(comm, compute) / total(comm)) if comm and total(comm) > 0 else None
+    ranked = sorted(by_name.items(), key=lambda kv: -sum(kv[1]))[:top]
+    return {"window_us": t1 - t0, "idle_us": (t1 - t0) - total(busy_all), "streams": streams, "classes": classes,
+            "comm_overlap": overlap, "comm_exposed_us": (total(comm) - intersect(comm, compute)) if comm else 0.0,
+            "top": [{"name": n, "sum_us": sum(d), "launches": len(d), "mean_us": sum(d) / len(d)} for n, d in ranked]}
+
+
+def render(rank: str, r: Dict) -> List[str]:
+    w = r["window_us"] or 1.0
+    out = [f"== {rank}: step window {w / 1e3:.2f} ms, all streams idle {r['idle_us'] / 1e3:.2f} ms ({100 * r['idle_us'] / w:.1f}%)"]
+    out.append("  stream            busy ms   share  launches")
+    for s, v in sorted(r["streams"].items(), key=lambda kv: -kv[1]["busy_us"]):
+        out.append(f"  {s:<14s}{v['busy_us'] / 1e3:11.2f}{100 * v['busy_us'] / w:7.1f}%{v['launches']:10d}")
+    out.append("  class              sum ms   share  launches")
+    for c, v in sorted(r["classes"].items(), key=lambda kv: -kv[1]["sum_us"]):
+        out.append(f"  {c:<14s}{v['sum_us'] / 1e3:11.2f}{100 * v['sum_us'] / w:7.1f}%{v['launches']:10d}")
+    if r["comm_overlap"] is not None:
+        out.append(f"  communication overlapped with compute: {100 * r['comm_overlap']:.1f}% "
+                   f"(exposed {r['comm_exposed_us'] / 1e3:.2f} ms)")
+    out.append("  top kernels         sum ms  launches   mean us  name")
+    for k in r["top"]:
+        out.append(f"  {k['sum_us'] / 1e3:17.2f}{k['launches']:10d}{k['mean_us']:10.1f}  {k['name'][:100]}")
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("path", type=Path, help="trace file or directory of trace_rank*.json[.gz]")
+    ap.add_argument("--top", type=int, default=25)
+    ap.add_argument("--json", type=Path, default=None)
+    a = ap.parse_args(argv)
+    files = [a.path] if a.path.is_file() else sorted(list(a.path.glob("trace_rank*.json.gz")) + list(a.path.glob("trace_rank*.json")))
+    if not files:
+        print(f"no traces under {a.path}")
+        return 1
+    results = {}
+    for f in files:
+        results[f.name.split(".")[0]] = analyze_events(load_events(f), a.top)
+    for rank, r in results.items():
+        print("\n".join(render(rank, r)))
+    if a.json:
+        a.json.write_text(json.dumps(results, indent=1))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

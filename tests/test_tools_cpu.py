@@ -1,0 +1,46 @@
+"""Developer tools: log comparison."""
+from pithtrain_b200.tools.validate_correctness import compare
+
+LINE = ("[2026-01-01 00:00:0{i}] step 0000000{i}/00000025 | step-time {t} sec | cross-entropy-loss {ce} | "
+        "load-balance-loss 1.02e-03 | tokens-per-second 15,942 | peak-gpu-memory 142.13 GB\n")
+
+
+def _write(path, ces, t="8.2"):
+    path.write_text("noise\n" + "".join(LINE.format(i=i + 1, t=t, ce=ce) for i, ce in enumerate(ces)))
+    return str(path)
+
+
+def test_compare_logs(tmp_path, capsys):
+    a = _write(tmp_path / "a.log", [12.34, 12.30, 12.25])
+    b = _write(tmp_path / "b.log", [12.341, 12.301, 12.249], t="7.9")
+    c = _write(tmp_path / "c.log", [12.34, 12.30, 12.90])
+    d = _write(tmp_path / "d.log", [12.34, 12.30])
+    rows = compare.parse_log(a)
+    assert sorted(rows) == [1, 2, 3] and rows[2]["cross-entropy-loss"] == 12.30 and rows[1]["tokens-per-second"] == 15942
+    assert rows[1]["load-balance-loss"] == 1.02e-3
+    assert compare.main([a, b, "--skip", "0"]) == 0
+    assert "step-time" in capsys.readouterr().out
+    assert compare.main([a, c]) == 1 and "step 3" in capsys.readouterr().out
+    assert compare.main([a, d]) == 1
+
+
+def test_profile_analyze(tmp_path, capsys):
+    import gzip
+    import json
+
+    from pithtrain_b200.tools.profile import analyze
+
+    ev = lambda name, cat, ts, dur, stream: {"ph": "X", "cat": cat, "name": name, "ts": ts, "dur": dur, "args": {"stream": stream}}
+    events = [ev("pt_gemm_kernel<128>", "kernel", 0, 100, 7), ev("rmsnorm_fwd", "kernel", 100, 50, 7),
+              ev("ncclDevKernel_SendRecv", "kernel", 50, 100, 13), ev("pt_gemm_kernel<128>", "kernel", 200, 100, 7),
+              ev("Memcpy DtoD", "gpu_memcpy", 320, 10, 7), {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "ts": 0, "dur": 5}]
+    with gzip.open(tmp_path / "trace_rank0.json.gz", "wt") as f:
+        json.dump({"traceEvents": events}, f)
+    r = analyze.analyze_events(analyze.load_events(tmp_path / "trace_rank0.json.gz"))
+    assert r["window_us"] == 330 and r["idle_us"] == 330 - (150 + 100 + 10)
+    assert r["classes"]["gemm"]["sum_us"] == 200 and r["classes"]["communication"]["launches"] == 1
+    assert abs(r["comm_overlap"] - 1.0) < 1e-9 and r["streams"]["7"]["launches"] == 4
+    assert r["top"][0]["name"].startswith("pt_gemm")
+    assert analyze.main([str(tmp_path), "--json", str(tmp_path / "o.json")]) == 0
+    assert "communication overlapped" in capsys.readouterr().out and (tmp_path / "o.json").exists()
+    assert analyze.intersect([(0, 10), (20, 30)], [(5, 25)]) == 10
