@@ -90,6 +90,9 @@ SIGS = {
     "pt_ep_wait_returned": "PIIP",
     "pt_ep_ack": "PIIP",
     "pt_axpby_bf16": "PPLFFP",
+    "pt_quant_rows": "PLPIPIIPPLP",
+    "pt_quant_blocks": "PIIIPPPPP",
+    "pt_gemm_fp8": "PPPIIIILLLLPLPPIIIIP",
 }
 
 _CT = {"P": c_void_p, "I": c_int, "L": c_longlong, "F": c_float}

@@ -25,6 +25,7 @@ class FP8WeightCacheControl:
     """
 
     version: int = 0
+    caches: List[dict] = []  # module-level caches registered by the fp8 operators
 
     @classmethod
     def step(cls) -> None:
@@ -36,6 +37,8 @@ class FP8WeightCacheControl:
             for m in module.modules():
                 if hasattr(m, "_wq_cache"):
                     m._wq_cache = None
+        for cache in cls.caches:
+            cache.clear()
 
 
 class WeightGradStore:

@@ -177,7 +177,7 @@ class Gate(nn.Module):
         if self.fp32_logits:
             return torch.nn.functional.linear(tokens.float(), self.weight.float(),
                                               None if self.bias is None else self.bias.float())
-        return linear(tokens, self.weight, self.bias)
+        return linear(tokens, self.weight, self.bias, fp8=False)
 
     def forward(self, tokens: torch.Tensor, reference: bool = False):
         """Returns ``(topk_idx[m,k] int32, topk_weight[m,k] fp32, lb_loss or None)``."""
@@ -331,6 +331,7 @@ class PipelineChunk(nn.Module):
         if self.stage_index == self.stage_count - 1:
             self.norm = self.build_norm(config)
             self.lm_head = Linear(H, V, bias=False)
+            self.lm_head.fp8 = False  # the vocabulary projection stays bf16
         ids = layer_partition(cfg_get(config, "num_hidden_layers"), self.stage_count, self.stage_index)
         self.layers = nn.ModuleDict({str(i): self.build_layer(config, i) for i in ids})
 

@@ -246,9 +246,10 @@ def setup_model(cfg: TrainingCfg, distributed_cfg: Any) -> None:
     from ..ops.linear import Linear
 
     training.Linear, training.GroupedLinear = Linear, GroupedLinear
-    if cfg.fp8:
-        from ..ops import fp8_linear
+    from ..ops import fp8_linear
 
+    fp8_linear.enable(bool(cfg.fp8))
+    if cfg.fp8:
         training.Linear, training.GroupedLinear = fp8_linear.FP8Linear, fp8_linear.FP8GroupedLinear
 
     cp = distributed.cp_size

@@ -46,13 +46,17 @@ class _GroupedLinearFn(torch.autograd.Function):
 
 
 def grouped_linear(x: torch.Tensor, weight: torch.Tensor, offs: torch.Tensor,
-                   weight_param: Optional[torch.Tensor] = None, grad_getter=None) -> torch.Tensor:
+                   weight_param: Optional[torch.Tensor] = None, grad_getter=None, fp8: Optional[bool] = None) -> torch.Tensor:
     """``y[rows of group g] = x[rows of group g] @ weight[g].T`` for ``weight[E, out, in]``."""
     wp = weight if weight_param is None else weight_param
     if grad_getter is None:
         grad_getter = lambda: grad_buffer(wp)  # noqa: E731
     if not x.requires_grad and torch.is_grad_enabled():
         x = x.detach().requires_grad_()
+    from . import fp8_linear
+
+    if fp8_linear.eligible(x, weight, fp8):
+        return fp8_linear.fp8_grouped_linear_apply(x, weight, offs, grad_getter)
     return _GroupedLinearFn.apply(x, weight, offs, grad_getter, True)
 
 
@@ -66,8 +70,10 @@ class GroupedLinear(nn.Module):
         self.weight = nn.Parameter(torch.empty((num_groups, out_features, in_features), device=device, dtype=dtype))
         nn.init.normal_(self.weight, std=0.02)
 
+    fp8: Optional[bool] = None
+
     def forward(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
-        return grouped_linear(x, self.weight, offs)
+        return grouped_linear(x, self.weight, offs, fp8=self.fp8)
 
     def extra_repr(self) -> str:
         return f"groups={self.num_groups}, in={self.in_features}, out={self.out_features}"

@@ -74,7 +74,7 @@ class _LinearFn(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           weight_param: Optional[torch.Tensor] = None, grad_getter=None) -> torch.Tensor:
+           weight_param: Optional[torch.Tensor] = None, grad_getter=None, fp8: Optional[bool] = None) -> torch.Tensor:
     """``x @ weight.T + bias`` with manual weight-gradient accumulation.
 
     ``weight`` may be a plain view covering several parameters; then ``grad_getter`` returns the
@@ -87,14 +87,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         # the weight gradient is produced inside backward(), which autograd only calls when some
         # input requires grad
         x = x.detach().requires_grad_()
+    from . import fp8_linear
+
+    if fp8_linear.eligible(x, weight, fp8):
+        return fp8_linear.fp8_linear_apply(x, weight, bias, (grad_getter, bias))
     return _LinearFn.apply(x, weight, bias, (grad_getter, bias))
 
 
 class Linear(nn.Linear):
     """``nn.Linear`` whose matmuls run on the sm_100a GEMM and whose wgrad can be deferred."""
 
+    fp8: Optional[bool] = None  # None: follow the global fp8 switch; False: always bf16; True: always fp8
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear(x, self.weight, self.bias)
+        return linear(x, self.weight, self.bias, fp8=self.fp8)
 
 
 class FusedWeights:

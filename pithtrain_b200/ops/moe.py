@@ -233,20 +233,38 @@ class _MoEExpertsFn(torch.autograd.Function):
         E = ew.w1.shape[0]
         offs, row_of_slot, slot_of_row = route_sort(eids, E, n_valid=(None if n_valid is None else n_valid * k))
         n_rows = offs[E:E + 1]
-        xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
-        gu = G.grouped_gemm_nt(xs, ew.w1, offs)
+        from . import fp8_linear as F8
+        from .quant import gemm_fp8_nt, quant_rows
+
+        fp8 = F8.eligible(x, ew.w1) and F8.eligible(x, ew.w2)
+        if fp8:
+            # gather into expert order and quantise in one pass; weights come from the per-step cache
+            q1, s1, _, _ = F8.quantized_weight(ew.w1)
+            xq, xsc = quant_rows(x, idx=slot_of_row, div=k, n_rows=n_rows)
+            gu = gemm_fp8_nt(xq, xsc, q1, s1, offs=offs)
+            del xq, xsc
+        else:
+            xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
+            gu = G.grouped_gemm_nt(xs, ew.w1, offs)
         gid = None
         if ew.b1 is not None:
             gid = rows_group_id(offs, gu.shape[0]).clamp(max=E - 1)
             gu = gu + ew.b1.detach()[gid].to(gu.dtype)
         act = swiglu_fwd(gu, n_rows, ew.interleaved, ew.alpha, ew.limit)
-        y = G.grouped_gemm_nt(act, ew.w2, offs)
+        if fp8:
+            q2, s2, _, _ = F8.quantized_weight(ew.w2)
+            aq, asc = quant_rows(act, n_rows=n_rows)
+            y = gemm_fp8_nt(aq, asc, q2, s2, offs=offs)
+            del aq, asc
+        else:
+            y = G.grouped_gemm_nt(act, ew.w2, offs)
         if ew.b2 is not None:
             y = y + ew.b2.detach()[gid].to(y.dtype)
         out = combine_rows(y, row_of_slot, k, w=w)
         ctx.save_for_backward(x, w, gu, offs, row_of_slot, slot_of_row)
         ctx.ew = ew
         ctx.k = k
+        ctx.fp8 = fp8
         return out
 
     @staticmethod
@@ -257,7 +275,16 @@ class _MoEExpertsFn(torch.autograd.Function):
         n_rows = offs[E:E + 1]
         d_out = d_out.contiguous()
         dyg = gather_rows(d_out, slot_of_row, div=k, n_rows=n_rows)  # unscaled d_out per sorted row
-        da = G.grouped_gemm_nn(dyg, ew.w2, offs)
+        if ctx.fp8:
+            from . import fp8_linear as F8
+            from .quant import gemm_fp8_nt, quant_rows
+
+            _, _, q2t, s2t = F8.quantized_weight(ew.w2)
+            dq, dsc = quant_rows(dyg, n_rows=n_rows)
+            da = gemm_fp8_nt(dq, dsc, q2t, s2t, offs=offs)
+            del dq, dsc
+        else:
+            da = G.grouped_gemm_nn(dyg, ew.w2, offs)
         w_ext = torch.cat([w.reshape(-1).float(), w.new_zeros(1, dtype=torch.float32)])
         row_w = w_ext[slot_of_row.long()]  # -1 (pad) picks the appended zero
         dgu, act_s, d_row_w = swiglu_bwd(gu, da, row_w, n_rows, ew.interleaved, ew.alpha, ew.limit,
@@ -272,7 +299,13 @@ class _MoEExpertsFn(torch.autograd.Function):
             accumulate_grad(ew.b1, segment_sum(dgu, offs, E))
         dw_ext = torch.cat([d_row_w, d_row_w.new_zeros(1)])
         d_w = dw_ext[row_of_slot.long()].view(w.shape).to(w.dtype)
-        dxs = G.grouped_gemm_nn(dgu, ew.w1, offs)
+        if ctx.fp8:
+            _, _, q1t, s1t = F8.quantized_weight(ew.w1)
+            gq, gsc = quant_rows(dgu, n_rows=n_rows)
+            dxs = gemm_fp8_nt(gq, gsc, q1t, s1t, offs=offs)
+            del gq, gsc
+        else:
+            dxs = G.grouped_gemm_nn(dgu, ew.w1, offs)
         d_x = combine_rows(dxs, row_of_slot, k) if ctx.needs_input_grad[0] else None
         del dxs
 
