@@ -191,16 +191,50 @@ def setup_dataset(cfg: TrainingCfg) -> None:
     training.dataset = ConcatDataset(shards, cfg.seed)
 
 
-def init_weights(model: nn.Module, num_layers: int, init_std: float = 0.02, depth_scaled: bool = True) -> None:
+def init_weights(model: nn.Module, num_layers: int, init_std: float = 0.02, depth_scaled: bool = True,
+                 seed: int = 0, expert_offset: int = 0) -> None:
     """N(0, init_std) for matrices; ``o_proj``/``down_proj`` get ``init_std/sqrt(2*num_layers)`` when
-    ``depth_scaled``; 1-D parameters are left as constructed."""
+    ``depth_scaled``; 1-D parameters are left as constructed.
+
+    The draw is a function of (seed, parameter name, global expert index) only, so the initial model
+    is the same whatever the pipeline / expert / data-parallel layout, replicas agree without a
+    broadcast, and experts on different ranks do not start as copies of one another. ``expert_offset``
+    is the global index of this rank's first local expert. (The reference draws from the rank's RNG
+    stream in module order, pithtrain/modules/training.py:297-325.)
+    """
+    import zlib
+
     out_std = init_std / math.sqrt(2.0 * num_layers) if depth_scaled else init_std
+    gens = {}
+
+    def gen_for(device) -> torch.Generator:
+        key = str(device)
+        if key not in gens:
+            gens[key] = torch.Generator(device=device)
+        return gens[key]
+
     with torch.no_grad():
         for name, p in model.named_parameters():
             if p.dim() < 2:
                 continue
             std = out_std if ("o_proj" in name or "down_proj" in name) else init_std
-            p.normal_(mean=0.0, std=std)
+            g = gen_for(p.device)
+            base = (int(seed) * 1000003 + zlib.crc32(name.encode())) % (1 << 62)
+            if ".experts." in name and p.dim() >= 2 and "shared" not in name:
+                for e in range(p.shape[0]):
+                    g.manual_seed(base * 4099 + expert_offset + e + 1)
+                    p[e].normal_(mean=0.0, std=std, generator=g)
+            else:
+                g.manual_seed(base * 4099)
+                p.normal_(mean=0.0, std=std, generator=g)
+
+
+def _num_experts(config) -> int:
+    for key in ("num_experts", "n_routed_experts", "num_local_experts"):
+        v = getattr(config, key, None)
+        if v:
+            return int(v)
+    return 0
 
 
 def materialize_small_params(model: nn.Module) -> None:
@@ -235,7 +269,8 @@ def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dty
                       expert_replica=(d.dp_group, d.dp_size), dense_replica=(d.dp_group, d.dp_size))
         else:
             raise ValueError(f"Unknown sharding_strategy: {sharding_strategy!r}")
-        groups.extend(build_shard_groups(m, grad_dtype=grad_dtype, prefix=f"module.{i}.", device=d.device, **kw))
+        groups.extend(build_shard_groups(m, grad_dtype=grad_dtype, prefix=f"module.{i}.", device=d.device,
+                                         expert_grad_divisor=d.ep_size, **kw))
     training.shard_groups = tuple(groups)
     return modules
 
@@ -278,7 +313,8 @@ def setup_model(cfg: TrainingCfg, distributed_cfg: Any) -> None:
     apply_fsdp(modules, getattr(distributed_cfg, "sharding_strategy", "fsdp"), gdt)
     for m in modules:
         materialize_small_params(m)
-        init_weights(m, config.num_hidden_layers, cfg.init_std, cfg.depth_scaled_init)
+        init_weights(m, config.num_hidden_layers, cfg.init_std, cfg.depth_scaled_init, seed=cfg.seed,
+                     expert_offset=distributed.ep_rank * (_num_experts(config) // max(distributed.ep_size, 1)))
     if hasattr(modules[0], "rotary_emb") and hasattr(modules[1], "rotary_emb"):
         modules[1].rotary_emb = modules[0].rotary_emb
 

@@ -86,6 +86,7 @@ class FlatShardGroup:
         self.name = name
         self.group, self.group_size, self.group_rank = group, group_size, group_rank
         self.replica_group, self.replica_size = replica_group, replica_size
+        self.grad_divisor = 1
         self.units = collect_units(named_params, fusions)
         self.named_params = list(named_params)
         if not self.units:
@@ -167,8 +168,18 @@ class FlatShardGroup:
             self.flat_grad.zero_()
 
     def scale_grads(self, scale) -> None:
+        """Multiply accumulated gradients by ``scale / grad_divisor``.
+
+        ``grad_divisor`` is the number of ranks whose tokens reached these parameters without being
+        averaged by :meth:`reduce_grads`: ``ep`` for expert parameters (every expert-parallel rank
+        feeds its own micro-batches into each expert, and expert gradients are only averaged over
+        dp×cp), 1 for the rest. With it every parameter receives the gradient of the same global
+        token-mean loss on every mesh. (The reference leaves expert gradients ``ep`` times larger,
+        pithtrain/tasks/pretrain_lm.py:393-396 together with the dp×cp expert mesh of
+        pithtrain/modules/training.py:364-370.)
+        """
         if self.flat_grad is not None:
-            self.flat_grad.mul_(scale)
+            self.flat_grad.mul_(scale / self.grad_divisor if self.grad_divisor != 1 else scale)
 
     def reduce_grads(self) -> None:
         """Average gradients over the shard group; afterwards only this rank's region is meaningful."""
@@ -242,7 +253,7 @@ def is_expert_param(name: str) -> bool:
 def build_shard_groups(module: nn.Module, *, expert_group=None, expert_group_size: int = 1, expert_group_rank: int = 0,
                        dense_group=None, dense_group_size: int = 1, dense_group_rank: int = 0,
                        grad_dtype: torch.dtype = torch.float32, expert_replica=(None, 1), dense_replica=(None, 1),
-                       prefix: str = "", device=None) -> List[FlatShardGroup]:
+                       prefix: str = "", device=None, expert_grad_divisor: int = 1) -> List[FlatShardGroup]:
     """Create the two shard groups (experts, everything else) of one model chunk."""
     named = [(prefix + n, p) for n, p in module.named_parameters() if p.requires_grad]
     fusions = find_fusions(module)
@@ -271,4 +282,5 @@ def build_shard_groups(module: nn.Module, *, expert_group=None, expert_group_siz
         groups.append(FlatShardGroup(prefix + "experts", ex, ex_f, expert_group, expert_group_size, expert_group_rank,
                                      grad_dtype, expert_replica[0], expert_replica[1], device=device,
                                      param_swapper=param_swapper))
+        groups[-1].grad_divisor = max(int(expert_grad_divisor), 1)
     return groups

@@ -159,9 +159,13 @@ def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], 
         dist.broadcast(num_tokens, src=dist.get_global_rank(d.pp_group, 0), group=d.pp_group)
     if loss is not None:
         loss = loss.sum() / num_tokens
-        if d.cp_size > 1:
-            dist.all_reduce(loss, group=d.cp_group)
-            loss /= d.cp_size
+        # mean over every rank that saw different tokens (the reference averages over cp only and logs
+        # the first data-parallel shard's loss, pithtrain/tasks/pretrain_lm.py:390; the global mean makes
+        # loss curves comparable across meshes)
+        width = d.dp_size * d.cp_size * d.ep_size
+        if width > 1:
+            dist.all_reduce(loss, group=d.dp_cp_ep_group)
+            loss /= width
 
     scale = 1.0 / num_tokens
     if training.shard_groups:

@@ -1,0 +1,45 @@
+"""The same job on different meshes must produce the same loss curve (gloo ranks on CPU).
+
+Covers the axes end to end through ``train_step``: data parallel with owner-sharded optimizer state (fsdp and
+hsdp placement), context parallel (zigzag batches + ring attention inside the model), expert and pipeline
+parallel, for AdamW and for Muon.
+"""
+import json
+
+import pytest
+
+from utilities import launch
+
+import train_worker
+
+
+def _curve(tmp_path, name, world, pp, ep, cp, strategy="fsdp", optimizer="adamw"):
+    out = tmp_path / f"{name}.json"
+    launch(world, train_worker.run, pp, ep, cp, strategy, str(out), optimizer, timeout=420.0)
+    return json.load(open(out))
+
+
+@pytest.fixture(scope="module")
+def baseline(tmp_path_factory):
+    return _curve(tmp_path_factory.mktemp("base"), "single", 1, 1, 1, 1)
+
+
+@pytest.mark.parametrize("name,world,pp,ep,cp,strategy", [
+    ("dp2", 2, 1, 1, 1, "fsdp"),
+    ("cp2", 2, 1, 1, 2, "fsdp"),
+    ("dp2_ep2_hsdp", 4, 1, 2, 1, "hsdp"),
+    ("pp2_cp2", 4, 2, 1, 2, "fsdp"),
+])
+def test_mesh_matches_single_process(tmp_path, baseline, name, world, pp, ep, cp, strategy):
+    got = _curve(tmp_path, name, world, pp, ep, cp, strategy)
+    assert len(got) == len(baseline)
+    for step, (a, b) in enumerate(zip(baseline, got)):
+        assert abs(a["loss"] - b["loss"]) < 2e-4 * abs(a["loss"]), (name, step, a, b)
+        assert abs(a["gradient_norm"] - b["gradient_norm"]) < 2e-3 * abs(a["gradient_norm"]), (name, step, a, b)
+
+
+def test_muon_dp2_ep2_matches_single_process(tmp_path):
+    a = _curve(tmp_path, "muon1", 1, 1, 1, 1, optimizer="muon")
+    b = _curve(tmp_path, "muon4", 4, 1, 2, 1, optimizer="muon")
+    for x, y in zip(a, b):
+        assert abs(x["loss"] - y["loss"]) < 1e-3 * abs(x["loss"]), (a, b)
