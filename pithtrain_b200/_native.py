@@ -90,6 +90,14 @@ SIGS = {
     "pt_ep_wait_returned": "PIIP",
     "pt_ep_ack": "PIIP",
     "pt_axpby_bf16": "PPLFFP",
+    "pt_fsdp_chan_struct_size": "",
+    "pt_fsdp_ctl_bytes": "",
+    "pt_fsdp_reduce_grid": "",
+    "pt_fsdp_signal_ready": "PIP",
+    "pt_fsdp_reduce_scatter": "PIFPP",
+    "pt_fsdp_wait_acks": "PIP",
+    "pt_fsdp_push_params": "PIP",
+    "pt_fsdp_wait_params": "PIP",
     "pt_quant_rows": "PLPIPIIPPLP",
     "pt_quant_blocks": "PIIIPPPPP",
     "pt_gemm_fp8": "PPPIIIILLLLPLPPIIIIP",

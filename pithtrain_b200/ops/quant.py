@@ -137,7 +137,9 @@ def gemm_fp8_nt(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: to
     G, N, _ = b3.shape
     if out is None:
         out = torch.empty((R, N), dtype=torch.bfloat16, device=a_q.device)
-    if use_native(a_q) and K % 16 == 0 and N % 8 == 0:
+    if a_q.is_cuda:
+        if K % 16 != 0 or N % 8 != 0:
+            raise ValueError(f"fp8 GEMM needs K % 16 == 0 and N % 8 == 0, got K={K}, N={N}")
         grouped = offs is not None
         rc = _native.lib().pt_gemm_fp8(a_q.data_ptr(), b3.data_ptr(), out.data_ptr(), 1 if grouped else 0, R, N, K,
                                        R, G * N, R, out.stride(0), a_s.data_ptr(), a_s.stride(0), b_s.data_ptr(),

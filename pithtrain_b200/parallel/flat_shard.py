@@ -82,7 +82,8 @@ def assign_owners(units: List[Unit], group_size: int) -> List[int]:
 class FlatShardGroup:
     def __init__(self, name: str, named_params: Sequence[Tuple[str, nn.Parameter]], fusions: Sequence[FusedWeights],
                  group=None, group_size: int = 1, group_rank: int = 0, grad_dtype: torch.dtype = torch.float32,
-                 replica_group=None, replica_size: int = 1, device=None, param_swapper=None) -> None:
+                 replica_group=None, replica_size: int = 1, device=None, param_swapper=None,
+                 fused_collectives: bool = True) -> None:
         self.name = name
         self.group, self.group_size, self.group_rank = group, group_size, group_rank
         self.replica_group, self.replica_size = replica_group, replica_size
@@ -106,8 +107,21 @@ class FlatShardGroup:
             u.offset = cursor[u.owner]
             cursor[u.owner] += u.padded
         total = self.region * group_size
-        self.flat_param = torch.zeros(total, dtype=self.param_dtype, device=device)
-        self.flat_grad = torch.zeros(total, dtype=grad_dtype, device=device)
+        self.comm = None
+        self._fused_sumsq = None
+        if fused_collectives and group_size > 1 and torch.device(device).type == "cuda":
+            from . import fsdp_fused
+
+            if fsdp_fused.usable(group, group_size, device):
+                # buffers live in symmetric memory: peers read gradient regions and write parameter
+                # regions directly, no NCCL reduce-scatter / all-gather
+                self.comm = fsdp_fused.FusedShardComm(group, group_size, group_rank, self.region, self.param_dtype,
+                                                      grad_dtype, device)
+        if self.comm is not None:
+            self.flat_param, self.flat_grad = self.comm.flat_param, self.comm.flat_grad
+        else:
+            self.flat_param = torch.zeros(total, dtype=self.param_dtype, device=device)
+            self.flat_grad = torch.zeros(total, dtype=grad_dtype, device=device)
         replaced: Dict[int, nn.Parameter] = {}
 
         def swap(old: nn.Parameter, new: nn.Parameter) -> None:
@@ -165,6 +179,8 @@ class FlatShardGroup:
 
     def zero_grad(self) -> None:
         if self.flat_grad is not None:
+            if self.comm is not None:
+                self.comm.before_zero_grad()  # owners may still be reading this rank's gradients
             self.flat_grad.zero_()
 
     def scale_grads(self, scale) -> None:
@@ -185,7 +201,12 @@ class FlatShardGroup:
         """Average gradients over the shard group; afterwards only this rank's region is meaningful."""
         if self.flat_grad is None:
             return
-        if self.group_size > 1:
+        self._fused_sumsq = None
+        if self.group_size > 1 and self.comm is not None:
+            sumsq = self.comm.reduce_scatter(1.0)
+            if self.replica_size == 1:
+                self._fused_sumsq = sumsq  # the reduction pass already measured the owned region
+        elif self.group_size > 1:
             mine = self.my_slice(self.flat_grad)
             backend = dist.get_backend(self.group)
             if backend == "nccl":
@@ -203,6 +224,9 @@ class FlatShardGroup:
     def owned_grad_sumsq(self) -> torch.Tensor:
         if self.flat_grad is None:
             return torch.zeros((), dtype=torch.float32)
+        if self._fused_sumsq is not None:
+            out, self._fused_sumsq = self._fused_sumsq, None
+            return out
         g = self.my_slice(self.flat_grad)
         if g.is_cuda and g.dtype in (torch.float32, torch.bfloat16) and g.numel() % 8 == 0:
             from .. import _native
@@ -221,6 +245,9 @@ class FlatShardGroup:
         """Publish the owners' updated regions to every rank of the shard group."""
         if self.flat_param is None or self.group_size == 1:
             return
+        if self.comm is not None:
+            self.comm.push_params()
+            return
         mine = self.my_slice(self.flat_param)
         backend = dist.get_backend(self.group)
         if backend == "nccl":
@@ -229,6 +256,11 @@ class FlatShardGroup:
             outs = [torch.empty_like(mine) for _ in range(self.group_size)]
             dist.all_gather(outs, mine.contiguous(), group=self.group)
             self.flat_param.copy_(torch.cat(outs))
+
+    def wait_params(self) -> None:
+        """Order later work of this stream after the arrival of every peer's published region."""
+        if self.comm is not None:
+            self.comm.before_forward()
 
     # ------------------------------------------------------------------ reporting
     def nbytes(self) -> int:

@@ -185,6 +185,8 @@ def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], 
         scheduler.step()
     for g in training.shard_groups:
         g.gather_params()
+    for g in training.shard_groups:
+        g.wait_params()
         g.zero_grad()
     MoELoadBalanceLossTracker.reset()
     return loss, gradient_norm
