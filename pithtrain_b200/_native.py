@@ -54,7 +54,7 @@ def lib() -> ctypes.CDLL:
 SIGS = {
     "pt_status_fetch_and_clear": "",
     "pt_sm_count": "",
-    "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIP",
+    "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIPILP",
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
     "pt_rmsnorm_bwd": "PPPPPPPIIIP",
@@ -63,7 +63,7 @@ SIGS = {
     "pt_qk_norm_rope_bwd": "PPPPPPPPPPPPIIIIILIP",
     "pt_router_topk_fwd": "PIPPPIIIIIFP",
     "pt_router_topk_bwd": "PPPPPPIIIIIIFP",
-    "pt_route_sort": "PPIIIPPPPIP",
+    "pt_route_sort": "PPIIIPLPPPIP",
     "pt_route_sort_noalloc": "PIIIPPPIP",
     "pt_gather_rows": "PPIPPIILP",
     "pt_combine": "PPPPPPIIIP",
@@ -124,7 +124,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 # Number of kernel launches issued through this module since it was last reset (bench bookkeeping).
 LAUNCHES = 0
-_LAUNCHES_PER_CALL = {"pt_route_sort": 3}
+_LAUNCHES_PER_CALL = {"pt_route_sort": 4}
 
 
 def check(rc: int, what: str) -> None:

@@ -43,6 +43,11 @@ struct GemmArgs {
   int use_tma_store;
   int epi;  // 0 staged coalesced rows, 1 direct per-thread rows, 2 TMA reduce-add when accumulating (else direct)
   int* err;
+  // A-operand row gather (K-major A only): tile row r reads source row a_idx[r] / a_idx_div, a negative
+  // index (or r >= a_idx_len) reads zeros. Replaces a separate gather pass over the activations.
+  const int* a_idx;
+  int a_idx_div;
+  long long a_idx_len;
 };
 
 struct TileInfo {
@@ -115,7 +120,7 @@ struct Scheduler {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool A_GATHER>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const GemmArgs args) {
@@ -157,7 +162,66 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (A_GATHER) {
+      // every lane gathers four rows of the A tile per k-block (32 x 4 = 128 rows); lane 0 also
+      // owns the barrier bookkeeping and the B tile
+      Scheduler<BN> sch(args);
+      TileInfo ti;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && sch.next(ti)) {
+        int grp = (args.mode == GEMM_DENSE) ? 0 : (int)ti.d_off;
+        int bn = ti.bn, bk = ti.bk;
+        if (args.mode == GEMM_MGROUP) {
+          if (B_MN) bk += grp * args.b_group_rows; else bn += grp * args.b_group_rows;
+        }
+        int r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          long long row = (long long)ti.am + 4 * lane + j;
+          int v = (row < args.a_idx_len && row < ti.row_end) ? args.a_idx[row] : -1;
+          r[j] = v >= 0 ? v / args.a_idx_div : -1;
+        }
+        for (int kb = 0; kb < ti.num_kb; ++kb, ++it) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          int good = 1;
+          if (lane == 0) good = mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER) ? 1 : 0;
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) { ok = false; break; }
+          if (lane == 0) mbar_expect_tx(&full[s], STAGE_BYTES);
+          __syncwarp();
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          int kk = kb * BK;
+          tma_gather4_2d(sa + lane * 512, &tmA, &full[s], ti.ak + kk, r[0], r[1], r[2], r[3]);
+          if (lane == 0) {
+            if (!B_MN) {
+              tma_load_2d(sb, &tmB, &full[s], bk + kk, bn);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (BK * 128), &tmB, &full[s], bn + 64 * j, bk + kk);
+            }
+          }
+        }
+      }
+      if (lane == 0 && *abort_flag) {
+        uint32_t n = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
+        for (uint32_t j = 0; j < n; ++j) {
+          uint32_t jt = it - 1 - j;
+          int s = jt % STAGES;
+          uint32_t ph = (jt / STAGES) & 1;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full[s], ph)) {
+            if (globaltimer_ns() - t0 > 20000000ull) {
+              if (args.err) atomicCAS(args.err, 0, PT_ERR_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
       Scheduler<BN> sch(args);
       TileInfo ti;
       uint32_t it = 0;
@@ -489,10 +553,10 @@ constexpr int gemm_smem_bytes() {
   return ((BN == 256) ? 4 : 6) * (A_TILE_BYTES + BN * BK * 2) + STAGING_BYTES + 256 + 1024;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool A_GATHER = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
                 const GemmArgs& args, int grid, cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, A_GATHER>;
   constexpr int smem = gemm_smem_bytes<BN>();
   static bool configured = false;
   if (!configured) {
@@ -514,13 +578,17 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
 //                    MN-major) into D + g*d_group_stride (always accumulates when accumulate=1;
 //                    groups with zero rows are left untouched). Group sizes must be multiples of 16.
 // a_rows/a_cols/lda etc. describe each operand as the row-major matrix it is in memory.
+// a_idx (optional, K-major A only): row r of the GEMM's A is source row a_idx[r] / a_idx_div of the
+// tensor described by a_rows/a_cols/lda (negative index or r >= a_idx_len: a zero row), fetched with
+// TMA gather4 straight into the swizzled operand tile.
 // Returns 0 on success.
 PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, int N, int K,
                         int a_mn, int b_mn, long long a_rows, long long a_cols, long long lda,
                         long long b_rows, long long b_cols, long long ldb, long long d_rows,
                         long long ldd, const int* offs, int num_groups, int b_group_rows,
                         long long d_group_stride, int out_fp32, int accumulate,
-                        int use_tma_store, int epi, int bn, int max_ctas, void* stream_) {
+                        int use_tma_store, int epi, int bn, int max_ctas, const int* a_idx, int a_idx_div,
+                        long long a_idx_len, void* stream_) {
   using namespace pt;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -528,7 +596,10 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
   if (bn != 128 && bn != 256) bn = (N >= 256) ? 256 : 128;
   CUtensorMap tmA, tmB, tmD;
   int rc;
-  if (!a_mn) rc = encode_tmap_2d(&tmA, A, TM_BF16, a_rows, a_cols, lda, BM, BK, TM_SW_128);
+  const bool gather = a_idx != nullptr;
+  if (gather && a_mn) return -3;  // row gather is implemented for K-major A only
+  if (gather) rc = encode_tmap_2d(&tmA, A, TM_BF16, a_rows, a_cols, lda, 1, BK, TM_SW_128);
+  else if (!a_mn) rc = encode_tmap_2d(&tmA, A, TM_BF16, a_rows, a_cols, lda, BM, BK, TM_SW_128);
   else rc = encode_tmap_2d(&tmA, A, TM_BF16, a_rows, a_cols, lda, BK, 64, TM_SW_128);
   if (rc) return 1000 + rc;
   if (!b_mn) rc = encode_tmap_2d(&tmB, B, TM_BF16, b_rows, b_cols, ldb, bn, BK, TM_SW_128);
@@ -558,6 +629,7 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
   args.use_tma_store = tma_store_ok ? 1 : 0;
   args.epi = epi;
   args.err = device_status_word();
+  args.a_idx = a_idx; args.a_idx_div = a_idx_div > 0 ? a_idx_div : 1; args.a_idx_len = a_idx_len;
 
   int sms = sm_count();
   int grid = sms;
@@ -568,6 +640,12 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
 
+  if (gather) {
+    if (bn == 256) return b_mn ? launch_gemm<256, false, true, true>(tmA, tmB, tmD, args, grid, stream)
+                               : launch_gemm<256, false, false, true>(tmA, tmB, tmD, args, grid, stream);
+    return b_mn ? launch_gemm<128, false, true, true>(tmA, tmB, tmD, args, grid, stream)
+                : launch_gemm<128, false, false, true>(tmA, tmB, tmD, args, grid, stream);
+  }
   int key = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (key) {
     case 0: return launch_gemm<128, false, false>(tmA, tmB, tmD, args, grid, stream);

@@ -4,14 +4,15 @@
 //   B [N,K] e4m3, one power-of-two scale per 128x128 tile        (weights, either orientation)
 //
 // The tensor cores run tcgen05.mma.kind::f8f6f4 over one 128-wide k-block at a time into one of
-// two TMEM buffers; the four epilogue warps pull each finished k-block partial out of TMEM and
+// two TMEM buffers; the eight epilogue warps pull each finished k-block partial out of TMEM and
 // fold it into fp32 register accumulators with that block's scale (sa[row,kb] * sb[tile,kb]) while
 // the tensor cores already work on the next k-block in the other buffer — two-level accumulation
 // with the promotion running concurrently with the MMAs instead of stalling them.
 //
 //   warp 0      TMA producer   : A and B k-blocks (128 rows x 128 bytes, 128B swizzle) into a ring
 //   warp 1      MMA issuer     : 4 x (M128 N128 K32) per k-block, commit -> smem stage free, TMEM full
-//   warps 2..5  promotion + epilogue: tcgen05.ld, scaled FMA, bf16 store (TMA store or direct rows)
+//   warps 2..9  promotion + epilogue: tcgen05.ld, scaled FMA, bf16 store (TMA store or direct rows);
+//               two warps per TMEM lane quarter, each owning one 64-column half of the tile
 //
 // Modes: dense, and M-grouped (expert GEMMs: rows grouped by a device-side offsets array, group g
 // uses weight rows [g*b_group_rows, ...)). Takes the role of DeepGEMM's fp8_gemm_nt and
@@ -28,9 +29,11 @@ constexpr int UMMA_K = 32;
 constexpr int TILE_BYTES = BM * BK;  // 16 KB per operand per stage
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int STAGES = 5;
-constexpr int EPI_WARPS = 4;
-constexpr int STAGING_BYTES = EPI_WARPS * 2 * 4096;
-constexpr uint32_t TMEM_COLS = 2 * BN;
+constexpr int EPI_WARPS = 8;  // two per TMEM lane quarter: each folds one 64-column half of the tile
+constexpr int STAGING_BYTES = EPI_WARPS * 4096;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int NBUF = 4;  // k-block accumulators in flight: hides the commit -> tcgen05.ld -> release round trip
+constexpr uint32_t TMEM_COLS = NBUF * BN;  // 512: the whole tensor memory of the SM
 constexpr uint32_t IDESC = make_idesc(0, 0, BM, BN, false, false);
 
 struct Args {
@@ -91,7 +94,7 @@ struct Sched {
   }
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const Args args) {
   extern __shared__ uint8_t smem_raw[];
@@ -100,8 +103,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
-  uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* tmem_empty = tmem_full + NBUF;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + NBUF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,7 +114,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    for (int b = 0; b < NBUF; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -169,8 +172,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = true;
       while (ok && sch.next(ti)) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          int buf = it & 1;
-          uint32_t bph = (it >> 1) & 1;
+          int buf = it % NBUF;
+          uint32_t bph = (it / NBUF) & 1;
           ok = mbar_wait_bounded(&tmem_empty[buf], bph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           int s = it % STAGES;
@@ -193,72 +196,76 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;  // which 64 columns of the tile this warp folds
+    constexpr int HC = BN / 2;
     Sched sch(args);
     Tile ti;
     uint32_t it = 0;
     bool used_tma = false, ok = true;
+    uint8_t* st = staging + (warp - 2) * 4096;
     while (ok && sch.next(ti)) {
       const int row = ti.row0 + q * 32 + lane;
       const bool rvalid = row < ti.row_end;
       const float* sa_p = args.sa + row;
       const float* sb_p = args.sb + ((long long)ti.grp * nblocks + ti.nt) * num_kb;
-      float acc[BN];
+      float acc[HC];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < HC; ++i) acc[i] = 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
+        const int buf = it % NBUF;
+        const uint32_t bph = (it / NBUF) & 1;
         const float sc = (rvalid ? sa_p[(long long)kb * args.ld_sa] : 0.f) * sb_p[kb];
-        ok = mbar_wait_bounded(&tmem_full[buf], bph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE);
+        // one lane polls the barrier, the warp follows: 8 pollers per CTA instead of 256
+        int good = 1;
+        if (lane == 0) good = mbar_wait_bounded(&tmem_full[buf], bph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        ok = good != 0;
         if (!ok) break;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c * 32 + j]);
-        }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * HC;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr, r0);
+        tmem_ld_32x32(taddr + 32, r1);
+        tmem_ld_wait();
+        // the partial is in registers: hand the TMEM buffer back before doing the arithmetic
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), sc, acc[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(r1[j]), sc, acc[32 + j]);
       }
       if (!ok) break;
       const bool full_tile = (args.mode == 0) ? (ti.row0 + BM <= args.M) : (ti.row0 + BM <= ti.row_end);
+      const int col0 = ti.col0 + half * HC;
+      if (col0 >= args.N) continue;  // uniform across the warp
       if (args.use_tma_store && full_tile) {
         used_tma = true;
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* rowp = st + lane * 128;
 #pragma unroll
-        for (int cc = 0; cc < BN / 64; ++cc) {
-          if (ti.col0 + cc * 64 < args.N) {
-            uint8_t* st = staging + (q * 2 + cc) * 4096;
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
-            uint8_t* rowp = st + lane * 128;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              uint4 v;
-              v.x = pack_bf16x2(acc[cc * 64 + 8 * j + 0], acc[cc * 64 + 8 * j + 1]);
-              v.y = pack_bf16x2(acc[cc * 64 + 8 * j + 2], acc[cc * 64 + 8 * j + 3]);
-              v.z = pack_bf16x2(acc[cc * 64 + 8 * j + 4], acc[cc * 64 + 8 * j + 5]);
-              v.w = pack_bf16x2(acc[cc * 64 + 8 * j + 6], acc[cc * 64 + 8 * j + 7]);
-              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmD, st, ti.col0 + cc * 64, ti.row0 + q * 32);
-              tma_store_commit();
-            }
-          }
+        for (int j = 0; j < 8; ++j) {
+          uint4 v;
+          v.x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
+          v.y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
+          v.z = pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]);
+          v.w = pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]);
+          *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmD, st, col0, ti.row0 + q * 32);
+          tma_store_commit();
         }
       } else if (rvalid) {
-        __nv_bfloat16* p = args.D + (long long)row * args.ldd + ti.col0;
+        __nv_bfloat16* p = args.D + (long long)row * args.ldd + col0;
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i) {
-          if (ti.col0 + 8 * i < args.N) {
+        for (int i = 0; i < HC / 8; ++i) {
+          if (col0 + 8 * i < args.N) {
             uint4 v;
             v.x = pack_bf16x2(acc[8 * i + 0], acc[8 * i + 1]);
             v.y = pack_bf16x2(acc[8 * i + 2], acc[8 * i + 3]);
@@ -325,6 +332,6 @@ PT_API int pt_gemm_fp8(const void* A, const void* B, void* D, int mode, int M, i
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_fp8_kernel<<<grid, 192, SMEM_BYTES, stream>>>(tmA, tmB, tmD, args);
+  gemm_fp8_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmD, args);
   return (int)cudaGetLastError();
 }

@@ -471,13 +471,137 @@ PT_API int pt_router_topk_bwd(const float* probs, const int* topk_idx, const flo
   return (int)cudaGetLastError();
 }
 
+// ----------------------------------------------------------------------------------------------
+// Routing sort, chunked form: O(n) work instead of one scan of all slots per expert.
+//   hist : every warp owns a chunk of ROUTE_CHUNK consecutive slots and counts experts in shared memory
+//   scan : per expert, exclusive prefix over the chunks (slot order) and the aligned group offsets
+//   place: every warp walks its chunk in slot order; match.any groups the lanes of one expert, so a
+//          slot's row is offs[e] + (slots of e in earlier chunks) + (earlier slots of e in this chunk)
+// The result is the same stable order as the per-expert kernels above.
+// ----------------------------------------------------------------------------------------------
+constexpr int ROUTE_CHUNK = 512;
+constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_MAX_E_SMEM = 1024;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_hist_kernel(const int* __restrict__ eids, const int* __restrict__ n_ptr, int n_max, int E,
+                  int* __restrict__ hist /* [chunks, E] */) {
+  extern __shared__ int sh[];  // [ROUTE_WARPS][E]
+  const int n = n_ptr ? min(*n_ptr, n_max) : n_max;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * ROUTE_WARPS + w;
+  int* my = sh + w * E;
+  for (int e = lane; e < E; e += 32) my[e] = 0;
+  __syncwarp();
+  const int begin = chunk * ROUTE_CHUNK, end = min(begin + ROUTE_CHUNK, n);
+  for (int i = begin + lane; i < end; i += 32) {
+    int e = eids[i];
+    if (e >= 0 && e < E) atomicAdd(&my[e], 1);
+  }
+  __syncwarp();
+  const int chunks = (n_max + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  if (chunk < chunks)
+    for (int e = lane; e < E; e += 32) hist[(long long)chunk * E + e] = my[e];
+}
+
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int* __restrict__ hist, int chunks, int E, int align, int* __restrict__ offs, int r_cap,
+                  int* __restrict__ err) {
+  __shared__ int padded[ROUTE_MAX_E_SMEM];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      int v = hist[(long long)c * E + e];
+      hist[(long long)c * E + e] = run;
+      run += v;
+    }
+    padded[e] = (run + align - 1) / align * align;
+    hist[(long long)chunks * E + e] = run;  // total per expert, kept after the chunk rows
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int b = 0;
+    for (int e = 0; e < E; ++e) { offs[e] = b; b += padded[e]; }
+    offs[E] = b;
+    if (b > r_cap && err) atomicCAS(err, 0, PT_ERR_CAPACITY);
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_place_chunk_kernel(const int* __restrict__ eids, const int* __restrict__ n_ptr, int n_max, int E,
+                         const int* __restrict__ hist, const int* __restrict__ offs,
+                         int* __restrict__ row_of_slot, int* __restrict__ slot_of_row, int r_cap) {
+  extern __shared__ int sh[];  // [ROUTE_WARPS][E] running position per expert
+  const int n = n_ptr ? min(*n_ptr, n_max) : n_max;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * ROUTE_WARPS + w;
+  const int chunks = (n_max + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  if (offs[E] > r_cap) return;  // capacity overflow was reported by the scan
+  int* run = sh + w * E;
+  if (chunk < chunks)
+    for (int e = lane; e < E; e += 32) run[e] = offs[e] + hist[(long long)chunk * E + e];
+  __syncwarp();
+  const int begin = chunk * ROUTE_CHUNK, end = min(begin + ROUTE_CHUNK, n);
+  for (int start = begin; start < end; start += 32) {
+    const int i = start + lane;
+    int e = (i < end) ? eids[i] : -1;
+    const bool valid = e >= 0 && e < E;
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1);
+    int base = valid ? run[e] : 0;
+    __syncwarp();
+    if (valid) {
+      const int r = base + __popc(peers & ((1u << lane) - 1));
+      row_of_slot[i] = r;
+      slot_of_row[r] = i;
+      if ((peers & ((1u << lane) - 1)) == 0) run[e] = base + __popc(peers);  // first lane of the group
+    } else if (i < end) {
+      row_of_slot[i] = -1;
+    }
+    __syncwarp();
+  }
+  // slots past the device-side count
+  const int hard_end = min(begin + ROUTE_CHUNK, n_max);
+  for (int i = max(begin, n) + lane; i < hard_end; i += 32) row_of_slot[i] = -1;
+}
+
+// Pad rows of every group and the rows past the last group get slot -1.
+__global__ void route_pad_kernel(const int* __restrict__ hist_totals, const int* __restrict__ offs, int E,
+                                 int* __restrict__ slot_of_row, int r_cap) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= r_cap) return;
+  const int end = min(offs[E], r_cap);
+  if (r >= end) { slot_of_row[r] = -1; return; }
+  // binary search for the group of row r
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (offs[mid] <= r) lo = mid; else hi = mid - 1;
+  }
+  if (r >= offs[lo] + hist_totals[lo]) slot_of_row[r] = -1;
+}
+
 // Stable sort of n slots by expert id into groups aligned to `align` rows.
 //   counts [E] scratch, offs [E+1], row_of_slot [n_max], slot_of_row [r_cap].
+//   With counts_len >= (ceil(n_max / 512) + 1) * E the chunked O(n) kernels run (4 launches), else the
+//   per-expert kernels (3 launches, counts_len >= E).
 PT_API int pt_route_sort(const int* eids, const int* n_ptr, int n_max, int E, int align,
-                         int* counts, int* offs, int* row_of_slot, int* slot_of_row, int r_cap,
+                         int* counts, long long counts_len, int* offs, int* row_of_slot, int* slot_of_row, int r_cap,
                          void* stream_) {
   cudaStream_t st = (cudaStream_t)stream_;
   if (E <= 0) return -1;
+  const int chunks = (n_max + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  if (counts_len >= (long long)(chunks + 1) * E && E <= ROUTE_MAX_E_SMEM && n_max > 0) {
+    // chunked sort; `counts` is the [chunks + 1, E] workspace
+    const int blocks = (chunks + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(int);
+    route_hist_kernel<<<blocks, ROUTE_WARPS * 32, smem, st>>>(eids, n_ptr, n_max, E, counts);
+    route_scan_kernel<<<1, 1024, 0, st>>>(counts, chunks, E, align, offs, r_cap, device_status_word());
+    route_place_chunk_kernel<<<blocks, ROUTE_WARPS * 32, smem, st>>>(eids, n_ptr, n_max, E, counts, offs, row_of_slot,
+                                                                     slot_of_row, r_cap);
+    if (r_cap > 0)
+      route_pad_kernel<<<(r_cap + 255) / 256, 256, 0, st>>>(counts + (long long)chunks * E, offs, E, slot_of_row, r_cap);
+    return (int)cudaGetLastError();
+  }
   route_count_kernel<<<E, ROUTE_THREADS, 0, st>>>(eids, n_ptr, n_max, E, counts);
   route_place_kernel<<<E, ROUTE_THREADS, 0, st>>>(eids, n_ptr, n_max, E, align, counts, offs,
                                                   row_of_slot, slot_of_row, r_cap, device_status_word());

@@ -41,29 +41,53 @@ def _owned(p: torch.Tensor) -> bool:
 def zeropower_via_newtonschulz5(Gm: torch.Tensor, steps: int = 5) -> torch.Tensor:
     """Quintic Newton-Schulz iteration towards the orthogonal polar factor, batched over leading dims.
 
-    Works on the wide orientation, pre-scales by the Frobenius norm so the spectral norm is <= 1, and
-    iterates ``X <- aX + (bA + cA^2)X`` with ``A = X X^T`` in bf16.
+    The iteration is ``X <- aX + (bA + cA^2)X`` with ``A = X X^T`` on the wide orientation of
+    ``X0 = G / (|G|_F + 1e-7)``, in bf16 (pithtrain/modules/optimizer.py:34-57 of the reference). It is
+    evaluated so that the large ``[m, n]`` operand is only ever touched by matrix products:
+
+    * ``aX + BX = (B + aI) X`` — the ``a`` goes onto the diagonal of the small ``[m, m]`` matrix, so no
+      copy of ``X`` is made for a ``beta`` term;
+    * the Frobenius normalisation is folded into the first step: ``A = s^2 G G^T`` and
+      ``X1 = (s (B + aI)) G`` with ``s = 1/(|G|_F + 1e-7)`` — ``G`` itself is never rescaled;
+    * a tall input is used through its transposed view and the last product is formed directly in the
+      input's orientation (``X^T (B + aI)``, the small factor being symmetric), so the result needs no
+      transposing copy.
     """
     assert Gm.ndim >= 2
     a, b, c = 3.4445, -4.7750, 2.0315
-    X = Gm.to(torch.bfloat16)
-    tall = Gm.size(-2) > Gm.size(-1)
-    if tall:
-        X = X.mT
-    nrm = torch.linalg.vector_norm(X, dim=(-2, -1), keepdim=True, dtype=torch.float32)
-    X = (X / (nrm + 1e-7).to(X.dtype))
-    batched = X.ndim == 3
-    for _ in range(steps):
-        A = X @ X.mT
-        if batched:
+    G = Gm.to(torch.bfloat16)
+    squeeze = G.ndim == 2
+    if squeeze:
+        G = G.unsqueeze(0)
+    lead = G.shape[:-2]
+    G = G.reshape(-1, G.shape[-2], G.shape[-1])
+    tall = G.size(-2) > G.size(-1)
+    X = G.mT if tall else G  # wide orientation [m, n], m <= n (a view)
+    if steps <= 0:
+        nrm = torch.linalg.vector_norm(G, dim=(-2, -1), keepdim=True, dtype=torch.float32)
+        out = G / (nrm + 1e-7).to(G.dtype)
+    else:
+        nrm = torch.linalg.vector_norm(G, dim=(-2, -1), keepdim=True, dtype=torch.float32)
+        s = 1.0 / (nrm + 1e-7)
+        s1, s2 = s.to(G.dtype), (s * s).to(G.dtype)
+        out = None
+        for it in range(steps):
+            A = torch.bmm(X, X.mT)
+            if it == 0:
+                A.mul_(s2)
             B = torch.baddbmm(A, A, A, beta=b, alpha=c)
-            X = torch.baddbmm(X, B, X, beta=a, alpha=1.0)
-        else:
-            B = torch.addmm(A, A, A, beta=b, alpha=c)
-            X = torch.addmm(X, B, X, beta=a, alpha=1.0)
-    if tall:
-        X = X.mT
-    return X
+            B.diagonal(dim1=-2, dim2=-1).add_(a)
+            if it == 0:
+                B.mul_(s1)
+            last = it == steps - 1
+            if last and tall:
+                out = torch.bmm(X.mT, B)  # [n, m]: the input's own orientation
+            else:
+                X = torch.bmm(B, X)
+                if last:
+                    out = X
+    out = out.reshape(*lead, out.shape[-2], out.shape[-1])
+    return out.squeeze(0) if squeeze else out
 
 
 def muon_scale_factor(n: int, m: int) -> float:

@@ -30,14 +30,16 @@ ACC_EPILOGUE = 2
 
 def _launch(a, b, d, mode, M, N, K, a_mn, b_mn, a_shape, lda, b_shape, ldb, d_rows, ldd,
             offs=None, num_groups=0, b_group_rows=0, d_group_stride=0, accumulate=False,
-            max_ctas=0):
+            max_ctas=0, a_idx=None, a_idx_div=1):
     L = _native.lib()
     out_fp32 = 1 if d.dtype == torch.float32 else 0
     rc = L.pt_gemm_bf16(
         a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, M, N, K, int(a_mn), int(b_mn),
         a_shape[0], a_shape[1], lda, b_shape[0], b_shape[1], ldb, d_rows, ldd,
         None if offs is None else offs.data_ptr(), num_groups, b_group_rows, d_group_stride,
-        out_fp32, int(accumulate), int(USE_TMA_STORE), ACC_EPILOGUE, FORCE_BN, max_ctas, _native.stream_ptr(),
+        out_fp32, int(accumulate), int(USE_TMA_STORE), ACC_EPILOGUE, FORCE_BN, max_ctas,
+        None if a_idx is None else a_idx.data_ptr(), int(a_idx_div), 0 if a_idx is None else a_idx.numel(),
+        _native.stream_ptr(),
     )
     _native.check(rc, "pt_gemm_bf16")
 
@@ -132,44 +134,58 @@ def _group_loop(offs: torch.Tensor):
 
 
 @torch.no_grad()
-def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+def _gathered(x: torch.Tensor, a_idx: torch.Tensor, div: int) -> torch.Tensor:
+    """Reference of the in-kernel row gather: ``x[a_idx // div]`` with zero rows for negative indices."""
+    ii = a_idx.long()
+    rows = x[(ii.clamp(min=0) // div)]
+    return torch.where((ii >= 0).unsqueeze(-1), rows, torch.zeros((), dtype=x.dtype, device=x.device))
+
+
+@torch.no_grad()
+def grouped_gemm_nt(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: torch.Tensor | None = None,
+                    a_idx: torch.Tensor | None = None, a_idx_div: int = 1) -> torch.Tensor:
     """Rows ``[offs[g], offs[g+1])`` of ``x[R,K]`` times ``w[g][N,K].T`` -> ``out[R,N]``.
 
-    Rows at or beyond ``offs[-1]`` are left untouched.
+    With ``a_idx`` (int32 ``[R]``) the GEMM's row ``r`` is ``x[a_idx[r] // a_idx_div]`` (zeros for a
+    negative index): the expert-order gather happens inside the TMA producer and the gathered copy of
+    the activations is never written. Rows at or beyond ``offs[-1]`` are left untouched.
     """
     G, N, K = w.shape
+    R = x.shape[0] if a_idx is None else int(a_idx.numel())
     if out is None:
-        out = torch.empty((x.shape[0], N), dtype=x.dtype, device=x.device)
+        out = torch.empty((R, N), dtype=x.dtype, device=x.device)
     if not _native_ok(x, w):
+        xs = x if a_idx is None else _gathered(x, a_idx, a_idx_div)
         for g, a, b in _group_loop(offs):
-            out[a:b] = (x[a:b].float() @ w[g].float().t()).to(out.dtype)
+            out[a:b] = (xs[a:b].float() @ w[g].float().t()).to(out.dtype)
         return out
     _chk2d(x, "x")
     assert w.is_contiguous() and w.dtype == torch.bfloat16 and offs.dtype == torch.int32
-    R = x.shape[0]
-    _launch(x, w, out, MGROUP, R, N, K, False, False, (R, K), x.stride(0), (G * N, K), K,
-            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N)
+    assert a_idx is None or (a_idx.dtype == torch.int32 and a_idx.is_contiguous())
+    _launch(x, w, out, MGROUP, R, N, K, False, False, (x.shape[0], K), x.stride(0), (G * N, K), K,
+            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N, a_idx=a_idx, a_idx_div=a_idx_div)
     return out
 
 
 @torch.no_grad()
-def grouped_gemm_nn(dy: torch.Tensor, w: torch.Tensor, offs: torch.Tensor,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
-    """Rows of group g of ``dy[R,N]`` times ``w[g][N,K]`` -> ``out[R,K]`` (expert dgrad)."""
+def grouped_gemm_nn(dy: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: torch.Tensor | None = None,
+                    a_idx: torch.Tensor | None = None, a_idx_div: int = 1) -> torch.Tensor:
+    """Rows of group g of ``dy[R,N]`` times ``w[g][N,K]`` -> ``out[R,K]`` (expert dgrad); ``a_idx`` gathers
+    the rows of ``dy`` inside the kernel as in :func:`grouped_gemm_nt`."""
     G, N, K = w.shape
+    R = dy.shape[0] if a_idx is None else int(a_idx.numel())
     if out is None:
-        out = torch.empty((dy.shape[0], K), dtype=dy.dtype, device=dy.device)
+        out = torch.empty((R, K), dtype=dy.dtype, device=dy.device)
     if not _native_ok(dy, w):
+        ds = dy if a_idx is None else _gathered(dy, a_idx, a_idx_div)
         for g, a, b in _group_loop(offs):
-            out[a:b] = (dy[a:b].float() @ w[g].float()).to(out.dtype)
+            out[a:b] = (ds[a:b].float() @ w[g].float()).to(out.dtype)
         return out
     _chk2d(dy, "dy")
     assert w.is_contiguous() and w.dtype == torch.bfloat16 and offs.dtype == torch.int32
     assert N % 64 == 0, "reduction dim of a grouped dgrad must be a multiple of 64"
-    R = dy.shape[0]
-    _launch(dy, w, out, MGROUP, R, K, N, False, True, (R, N), dy.stride(0), (G * N, K), K,
-            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N)
+    _launch(dy, w, out, MGROUP, R, K, N, False, True, (dy.shape[0], N), dy.stride(0), (G * N, K), K,
+            R, out.stride(0), offs=offs, num_groups=G, b_group_rows=N, a_idx=a_idx, a_idx_div=a_idx_div)
     return out
 
 

@@ -20,6 +20,7 @@ wgrad.
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -84,12 +85,13 @@ def route_sort(eids: torch.Tensor, num_experts: int, r_cap: Optional[int] = None
     flat = flat.int() if flat.dtype != torch.int32 else flat
     flat = flat.contiguous()
     dev = flat.device
-    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    chunks = (n + 511) // 512
+    counts = torch.empty((chunks + 1) * num_experts, dtype=torch.int32, device=dev)  # workspace of the chunked sort
     offs = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     row_of_slot = torch.empty(n, dtype=torch.int32, device=dev)
     slot_of_row = torch.empty(r_cap, dtype=torch.int32, device=dev)
     rc = L.pt_route_sort(flat.data_ptr(), None if n_valid is None else n_valid.data_ptr(), n, num_experts,
-                         ALIGN, counts.data_ptr(), offs.data_ptr(), row_of_slot.data_ptr(),
+                         ALIGN, counts.data_ptr(), counts.numel(), offs.data_ptr(), row_of_slot.data_ptr(),
                          slot_of_row.data_ptr(), r_cap, sp())
     _native.check(rc, "pt_route_sort")
     return offs, row_of_slot, slot_of_row
@@ -211,6 +213,10 @@ def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------
 # fused expert block
 # ------------------------------------------------------------------------------------------------
+# Fuse the expert-order gather into the A-operand load of the first expert GEMM.
+GATHER_IN_GEMM = os.environ.get("PITHTRAIN_GATHER_IN_GEMM", "0") == "1"
+
+
 class ExpertWeights:
     """What :func:`moe_experts` needs from the owning module.
 
@@ -243,6 +249,10 @@ class _MoEExpertsFn(torch.autograd.Function):
             xq, xsc = quant_rows(x, idx=slot_of_row, div=k, n_rows=n_rows)
             gu = gemm_fp8_nt(xq, xsc, q1, s1, offs=offs)
             del xq, xsc
+        elif GATHER_IN_GEMM and use_native(x) and x.shape[1] % 64 == 0:
+            # the first expert GEMM reads token rows through the index (TMA gather4): the expert-ordered
+            # copy of the activations is never materialised
+            gu = G.grouped_gemm_nt(x, ew.w1, offs, a_idx=slot_of_row, a_idx_div=k)
         else:
             xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
             gu = G.grouped_gemm_nt(xs, ew.w1, offs)

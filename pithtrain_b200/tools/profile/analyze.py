@@ -106,7 +106,15 @@ def analyze_events(events: List[dict], top: int = 25) -> Dict:
     busy_all = union((e["ts"], e["ts"] + e["dur"]) for e in events)
     streams = {s: {"busy_us": total(union(iv)), "launches": len(iv)} for s, iv in by_stream.items()}
     comm = union((e["ts"], e["ts"] + e["dur"]) for e in by_class.get("communication", []))
-    comm_streams = {str(e["stream"]) for e in by_class.get("communication", [])}
+    # a stream counts as a communication stream when most of its busy time is communication kernels
+    # (a stray collective on the compute stream must not turn it into one)
+    comm_time: Dict[str, float] = defaultdict(float)
+    all_time: Dict[str, float] = defaultdict(float)
+    for e in events:
+        all_time[str(e["stream"])] += e["dur"]
+        if e["cls"] == "communication":
+            comm_time[str(e["stream"])] += e["dur"]
+    comm_streams = {s for s, t in comm_time.items() if t > 0.5 * all_time[s]}
     compute = union((e["ts"], e["ts"] + e["dur"]) for e in events
                     if e["cls"] in ("gemm", "attention", "other", "optimizer") and str(e["stream"]) not in comm_streams)
     classes = {c: {"sum_us": sum(e["dur"] for e in evs), "launches": len(evs)} for c, evs in by_class.items()}

@@ -201,3 +201,18 @@ def test_moe_experts_vs_loop():
     assert calc_diff(w.grad, wr.grad) < 1e-3
     assert calc_diff(g1, w1r.grad) < 1e-3
     assert calc_diff(g2, w2r.grad) < 1e-3
+
+
+@pytest.mark.parametrize("n,k,E,valid", [(2048, 8, 128, 1000), (700, 4, 16, 699), (64, 2, 8, 0)])
+def test_route_sort_device_side_count(n, k, E, valid):
+    """Slots at or past a device-side count are ignored (the fused EP transport sizes by capacity)."""
+    torch.manual_seed(4)
+    eids = torch.randint(0, E, (n, k), device="cuda", dtype=torch.int32)
+    nv = torch.tensor([valid * k], device="cuda", dtype=torch.int32)
+    offs, ros, sor = M.route_sort(eids, E, n_valid=nv)
+    ref_in = eids.cpu().clone().view(-1)
+    ref_in[valid * k:] = -1
+    offs_r, ros_r, sor_r = M.route_sort_ref(ref_in, E, sor.numel())
+    _native.check_status()
+    assert torch.equal(offs.cpu(), offs_r) and torch.equal(ros.cpu(), ros_r)
+    assert torch.equal(sor.cpu(), sor_r)

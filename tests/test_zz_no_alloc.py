@@ -28,7 +28,7 @@ def _regular(L, eids, E, align, r_cap):
     offs = torch.empty(E + 1, dtype=torch.int32, device=dev)
     ros = torch.empty(n, dtype=torch.int32, device=dev)
     sor = torch.empty(r_cap, dtype=torch.int32, device=dev)
-    rc = L.pt_route_sort(eids.data_ptr(), None, n, E, align, counts.data_ptr(), offs.data_ptr(), ros.data_ptr(),
+    rc = L.pt_route_sort(eids.data_ptr(), None, n, E, align, counts.data_ptr(), counts.numel(), offs.data_ptr(), ros.data_ptr(),
                          sor.data_ptr(), r_cap, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     return offs, ros, sor
