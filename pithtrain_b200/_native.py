@@ -82,6 +82,9 @@ SIGS = {
     "pt_ipc_close": "P",
     "pt_ipc_handle_size": "",
     "pt_can_access_peer": "II",
+    "pt_symm_signal": "PIIIP",
+    "pt_symm_wait": "PIIIP",
+    "pt_symm_copy": "PPLIP",
     "pt_ep_chan_struct_size": "",
     "pt_ep_plan": "PIIIIIPPPPP",
     "pt_ep_push": "PIIPLPPPPPP",

@@ -45,3 +45,95 @@ PT_API int pt_can_access_peer(int dev, int peer) {
   if (cudaDeviceCanAccessPeer(&ok, dev, peer) != cudaSuccess) return 0;
   return ok;
 }
+
+// ----------------------------------------------------------------------------------------------
+// Building blocks for protocols over symmetric memory: system-scope flag words and bulk copies
+// whose source or destination may be a peer mapping. Every wait is bounded and reports through the
+// library's status word (code PT_ERR_TIMEOUT_PEER).
+// ----------------------------------------------------------------------------------------------
+#include "ptx.cuh"
+
+namespace pt {
+namespace symm {
+
+constexpr int MAXW = 32;
+struct PtrList {
+  unsigned* p[MAXW];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// word `index` of every listed control block = value, ordered after all earlier work of the stream
+__global__ void signal_kernel(PtrList ctl, int n, int index, unsigned value) {
+  __threadfence_system();
+  if ((int)threadIdx.x < n) st_release_sys(ctl.p[threadIdx.x] + index, value);
+}
+
+// wait until words [index, index + count) of the local control block are >= value (wrap-safe)
+__global__ void wait_kernel(const unsigned* ctl, int index, int count, unsigned value, int* err) {
+  if ((int)threadIdx.x >= count) return;
+  const unsigned* p = ctl + index + threadIdx.x;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if ((int)(ld_acquire_sys(p) - value) >= 0) return;
+    if ((it & 255u) == 255u) {
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > PT_WAIT_LIMIT_NS) {
+        if (err) atomicCAS(err, 0, PT_ERR_TIMEOUT_PEER);
+        return;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+// dst[0:bytes) = src[0:bytes), 16-byte vectors; loads bypass L1 so a peer's fresh data is seen
+__global__ void __launch_bounds__(256) copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i));
+    dst[i] = v;
+  }
+}
+
+}  // namespace symm
+}  // namespace pt
+
+// ctl_ptrs: host array of n device pointers (control blocks, own and peers').
+PT_API int pt_symm_signal(const void* const* ctl_ptrs, int n, int index, unsigned value, void* stream) {
+  using namespace pt::symm;
+  if (n <= 0 || n > MAXW) return -1;
+  PtrList l;
+  for (int i = 0; i < n; ++i) l.p[i] = reinterpret_cast<unsigned*>(const_cast<void*>(ctl_ptrs[i]));
+  signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(l, n, index, value);
+  return (int)cudaGetLastError();
+}
+
+PT_API int pt_symm_wait(const void* ctl, int index, int count, unsigned value, void* stream) {
+  using namespace pt::symm;
+  if (count <= 0 || count > MAXW) return -1;
+  wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const unsigned*>(ctl), index, count, value,
+                                                                   pt::device_status_word());
+  return (int)cudaGetLastError();
+}
+
+PT_API int pt_symm_copy(void* dst, const void* src, long long bytes, int max_ctas, void* stream) {
+  using namespace pt::symm;
+  if (bytes <= 0) return 0;
+  if (bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  long long nvec = bytes / 16;
+  long long blocks = (nvec + 255) / 256;
+  int cap = max_ctas > 0 ? max_ctas : pt::sm_count() * 4;
+  int grid = (int)(blocks < cap ? blocks : cap);
+  copy_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<uint4*>(dst),
+                                                                        reinterpret_cast<const uint4*>(src), nvec);
+  return (int)cudaGetLastError();
+}

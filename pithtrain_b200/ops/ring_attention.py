@@ -144,6 +144,69 @@ def _wait(reqs) -> None:
         r.wait()
 
 
+class _NcclRing:
+    """Payload moves one hop per step around the ring (``batch_isend_irecv``)."""
+
+    def __init__(self, payload, group, cp: int, rank: int):
+        self.cur, self.group, self.cp, self.rank = payload, group, cp, rank
+        self.nxt, self.reqs = None, []
+
+    def begin_step(self, i: int):
+        if i < self.cp - 1:
+            self.nxt, self.reqs = _rotate(self.cur, self.group, self.cp, self.rank)
+        return self.cur
+
+    def end_step(self, i: int) -> None:
+        _wait(self.reqs)
+        self.reqs = []
+        if self.nxt is not None:
+            self.cur, self.nxt = self.nxt, None
+
+    def finish(self) -> None:
+        pass
+
+
+class _PeerPull:
+    """Payload is published once in symmetric memory; step ``i`` reads rank ``rank - i`` directly, with the
+    next step's block being fetched on a side stream meanwhile (pithtrain_b200/parallel/cp_fused.py)."""
+
+    def __init__(self, kind: str, payload, group, cp: int, rank: int, with_grads: bool):
+        from ..parallel.cp_fused import get_exchange
+
+        self.cp, self.rank, self.local = cp, rank, payload
+        self.ex = get_exchange(kind, group, cp, rank, payload, with_grads)
+        self.epoch = self.ex.publish(payload)
+        self.pending = None
+
+    def begin_step(self, i: int):
+        if i == 0:
+            cur = self.local
+        else:
+            cur, ev = self.pending
+            torch.cuda.current_stream().wait_event(ev)
+        self.pending = self.ex.pull((self.rank - i - 1) % self.cp, self.epoch) if i < self.cp - 1 else None
+        return cur
+
+    def end_step(self, i: int) -> None:
+        pass
+
+    def finish(self) -> None:
+        self.ex.finish(self.epoch)
+
+
+_PULL_OK: dict = {}
+
+
+def _peer_pull_usable(group, cp: int, device) -> bool:
+    """Decided once per (group, device): the vote inside is a collective."""
+    key = (id(group), cp, str(device))
+    if key not in _PULL_OK:
+        from ..parallel import cp_fused
+
+        _PULL_OK[key] = cp_fused.usable(group, cp, device)
+    return _PULL_OK[key]
+
+
 def _pairs(cp: int, rank: int, src: int, block: int, window_left: Optional[int]):
     """(q half, k half, relation, q block id, k block id) for local queries vs the payload of ``src``."""
     out = []
@@ -166,12 +229,12 @@ class _RingAttention(torch.autograd.Function):
         q_halves = (q[:, :block], q[:, block:])
         outs: List[Optional[torch.Tensor]] = [None, None]
         lses: List[Optional[torch.Tensor]] = [None, None]
-        cur = [t.detach() for t in payload]
+        start = [t.detach() for t in payload]
+        pull = q.is_cuda and cp > 1 and _peer_pull_usable(group, cp, dev)
+        ring = _PeerPull("fwd", start, group, cp, rank, False) if pull else _NcclRing(start, group, cp, rank)
         for i in range(cp):
             src = (rank - i) % cp
-            nxt, reqs = (None, [])
-            if i < cp - 1:
-                nxt, reqs = _rotate(cur, group, cp, rank)
+            cur = ring.begin_step(i)
             with torch.no_grad():
                 k, v = expand(cur, params) if expand is not None else (cur[0], cur[1])
                 k_halves, v_halves = (k[:, :block], k[:, block:]), (v[:, :block], v[:, block:])
@@ -179,9 +242,8 @@ class _RingAttention(torch.autograd.Function):
                     mask = None if rel == "full" else block_mask(_positions(qb, block, dev), _positions(kb, block, dev), window_left)
                     o_p, lse_p = block_fwd(q_halves[qi], k_halves[ki], v_halves[ki], scale, mask)
                     outs[qi], lses[qi] = merge_partial(outs[qi], lses[qi], o_p, lse_p)
-            _wait(reqs)
-            if nxt is not None:
-                cur = nxt
+            ring.end_step(i)
+        ring.finish()
         out = torch.cat(outs, dim=1)
         lse = torch.cat(lses, dim=2)
         if sinks is not None:
@@ -206,14 +268,17 @@ class _RingAttention(torch.autograd.Function):
         halves = lambda t, dim=1: (t.narrow(dim, 0, block), t.narrow(dim, block, block))
         q_h, do_h, out_h, lse_h = halves(q), halves(do), halves(out), halves(lse, 2)
         dq = [torch.zeros(B, block, Hq, q.shape[-1], dtype=torch.float32, device=dev) for _ in range(2)]
-        cur = [t.detach() for t in payload]
+        start = [t.detach() for t in payload]
+        pull = q.is_cuda and cp > 1 and _peer_pull_usable(group, cp, dev)
+        ring = _PeerPull("bwd", start, group, cp, rank, True) if pull else _NcclRing(start, group, cp, rank)
         dacc = [torch.zeros(t.shape, dtype=torch.float32, device=dev) for t in payload]
         dparams = [torch.zeros(p.shape, dtype=torch.float32, device=dev) for p in params]
+        local_part = None
         for i in range(cp):
             src = (rank - i) % cp
-            nxt, reqs = (None, [])
-            if i < cp - 1:
-                nxt, reqs = _rotate(cur, group, cp, rank)
+            cur = ring.begin_step(i)
+            if pull:
+                dacc = [torch.zeros(t.shape, dtype=torch.float32, device=dev) for t in payload]
             with torch.enable_grad():
                 leaves = [t.detach().requires_grad_(t.is_floating_point()) for t in cur]
                 p_leaves = [p.detach().requires_grad_() for p in params]
@@ -240,12 +305,20 @@ class _RingAttention(torch.autograd.Function):
                 for j, g in enumerate(grads[n_payload:]):
                     if g is not None:
                         dparams[j] += g.float()
-            _wait(reqs)
-            # the gradient accumulators follow their payload around the ring and end at its owner
-            dacc, reqs2 = _rotate(dacc, group, cp, rank)
-            _wait(reqs2)
-            if nxt is not None:
-                cur = nxt
+            ring.end_step(i)
+            if pull:
+                # the partial goes straight to the owner of the block (own block: kept)
+                if i == 0:
+                    local_part = dacc
+                else:
+                    ring.ex.push_grad(src, ring.epoch, dacc)
+            else:
+                # the gradient accumulators follow their payload around the ring and end at its owner
+                dacc, reqs2 = _rotate(dacc, group, cp, rank)
+                _wait(reqs2)
+        ring.finish()
+        if pull:
+            dacc = ring.ex.collect_grads(ring.epoch, local_part)
         d_sinks = None
         if sinks is not None:
             delta = (do.float() * out.float()).sum(-1).permute(0, 2, 1)  # [B,Hq,S]

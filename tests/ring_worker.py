@@ -13,18 +13,34 @@ def zigzag_slice(x, cp, r, dim=1):
     return torch.cat([x.narrow(dim, r * b, b), x.narrow(dim, (2 * cp - 1 - r) * b, b)], dim=dim)
 
 
-def run(rank, world, case):
+def run(rank, world, case, device_type="cpu", rounds=1):
+    """``rounds`` > 2 exercises the slot reuse of the peer-memory transport on GPUs."""
+    for it in range(rounds):
+        _run_once(rank, world, case, device_type, first=(it == 0), seed=3 + it)
+    if device_type == "cuda":
+        from pithtrain_b200 import _native
+
+        torch.cuda.synchronize()
+        _native.check_status()
+
+
+def _run_once(rank, world, case, device_type, first, seed):
     from pithtrain_b200.contexts import distributed
     from pithtrain_b200.modules.distributed import DistributedCfg, setup_distributed
     from pithtrain_b200.ops.attention import attention_ref
     from pithtrain_b200.ops.ring_attention import mla_ring_attention_func, ring_attention_func
     from utilities import calc_diff
 
-    cfg = SimpleNamespace(distributed=DistributedCfg())
-    cfg.distributed.context_parallel_size = world
-    setup_distributed(cfg, failfast=False)
+    if first:
+        cfg = SimpleNamespace(distributed=DistributedCfg())
+        cfg.distributed.context_parallel_size = world
+        setup_distributed(cfg, failfast=False)
     cp, r = world, distributed.cp_rank
-    torch.manual_seed(3)
+    torch.manual_seed(seed)
+    if device_type == "cuda":
+        torch.set_default_device(distributed.device)
+        torch.backends.cuda.matmul.allow_tf32 = False  # the oracle comparison wants real fp32 products
+    tol = 1e-9 if device_type == "cpu" else 1e-5  # TF32-free fp32 on the GPU, different reduction order
     B, S = 2, 16 * cp
     if case == "mla":
         H, nope, rope, vd, lat = 3, 8, 4, 6, 10
@@ -43,12 +59,12 @@ def run(rank, world, case):
         Wp = torch.nn.Parameter(W.clone())
         out = mla_ring_attention_func(mine[0], mine[1], mine[2], mine[3], Wp, scale, nope, vd)
         out.backward(zigzag_slice(go, cp, r))
-        assert calc_diff(out, zigzag_slice(ref.detach(), cp, r)) < 1e-9
+        assert calc_diff(out, zigzag_slice(ref.detach(), cp, r)) < tol
         for a, b in zip(mine, leaves[:4]):
-            assert calc_diff(a.grad, zigzag_slice(b.grad, cp, r)) < 1e-9
+            assert calc_diff(a.grad, zigzag_slice(b.grad, cp, r)) < tol
         gW = Wp.grad.clone()
         dist.all_reduce(gW, group=distributed.cp_group)
-        assert calc_diff(gW, leaves[4].grad) < 1e-9
+        assert calc_diff(gW, leaves[4].grad) < tol
         return
     Hq, Hkv, D = (4, 2, 8) if case != "mha" else (2, 2, 8)
     window = 5 if case == "window_sink" else None
@@ -63,10 +79,10 @@ def run(rank, world, case):
     sp = torch.nn.Parameter(sinks.clone()) if sinks is not None else None
     out = ring_attention_func(mine[0], mine[1], mine[2], window_left=window, sinks=sp)
     out.backward(zigzag_slice(go, cp, r))
-    assert calc_diff(out, zigzag_slice(ref.detach(), cp, r)) < 1e-9, calc_diff(out, zigzag_slice(ref.detach(), cp, r))
+    assert calc_diff(out, zigzag_slice(ref.detach(), cp, r)) < tol, calc_diff(out, zigzag_slice(ref.detach(), cp, r))
     for a, b in zip(mine, leaves[:3]):
-        assert calc_diff(a.grad, zigzag_slice(b.grad, cp, r)) < 1e-9
+        assert calc_diff(a.grad, zigzag_slice(b.grad, cp, r)) < tol
     if sinks is not None:
         gs = sp.grad.clone()
         dist.all_reduce(gs, group=distributed.cp_group)
-        assert calc_diff(gs, leaves[3].grad) < 1e-8
+        assert calc_diff(gs, leaves[3].grad) < 10 * tol

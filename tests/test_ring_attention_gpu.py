@@ -1,0 +1,17 @@
+"""Ring attention on GPUs: the payload travels through symmetric peer memory (publish / pull / gradient push)."""
+import pytest
+import torch
+
+from utilities import launch
+
+import ring_worker
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("case", ["gqa", "window_sink", "mla"])
+def test_ring_attention_peer_pull(case):
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    launch(n, ring_worker.run, case, "cuda", 4, backend="nccl")
