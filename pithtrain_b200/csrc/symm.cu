@@ -95,9 +95,25 @@ __global__ void wait_kernel(const unsigned* ctl, int index, int count, unsigned 
   }
 }
 
-// dst[0:bytes) = src[0:bytes), 16-byte vectors; loads bypass L1 so a peer's fresh data is seen
+// dst[0:bytes) = src[0:bytes), 16-byte vectors; loads bypass L1 so a peer's fresh data is seen.
+// Eight independent loads are in flight per thread before the first store: a load over NVLink takes
+// microseconds, and a copy that is limited to a few dozen CTAs (to leave the SMs to compute kernels)
+// still has to cover the link's bandwidth-delay product.
 __global__ void __launch_bounds__(256) copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long nvec) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  constexpr int U = 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < nvec; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                   : "l"(src + i + u * stride));
+#pragma unroll
+    for (int u = 0; u < U; ++u) dst[i + u * stride] = v[u];
+  }
+  for (; i < nvec; i += stride) {
     uint4 v;
     asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i));
     dst[i] = v;

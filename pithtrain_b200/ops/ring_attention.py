@@ -46,9 +46,56 @@ def block_mask(q_pos: torch.Tensor, k_pos: torch.Tensor, window_left: Optional[i
     return m
 
 
-def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+# Blocks that need no explicit mask (fully visible, or the causal diagonal block) go to the library flash
+# kernel on GPUs, which returns the log-sum-exp the merge needs; everything else uses the fp32 math below.
+USE_LIBRARY_BLOCKS = True
+_LIB_BLOCKS_BROKEN = False
+
+
+def _lib_block_ok(q, k, v) -> bool:
+    return (USE_LIBRARY_BLOCKS and not _LIB_BLOCKS_BROKEN and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)
+            and q.shape[-1] == v.shape[-1] and q.shape[-1] % 8 == 0 and q.shape[-1] <= 256)
+
+
+def _to_bhsd(t: torch.Tensor, Hq: int) -> torch.Tensor:
+    return _expand_kv(t, Hq).permute(0, 2, 1, 3)
+
+
+def _lib_block_fwd(q, k, v, scale: float, causal: bool):
+    Hq = q.shape[2]
+    res = torch.ops.aten._scaled_dot_product_flash_attention(_to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq), 0.0, causal,
+                                                             False, scale=scale)
+    out, lse = res[0], res[1]
+    return out.permute(0, 2, 1, 3).float(), lse.float()
+
+
+def _lib_block_bwd(do, q, k, v, out, lse, scale: float, causal: bool):
+    Hq, Hkv = q.shape[2], k.shape[2]
+    B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
+    empty = torch.empty(0, dtype=torch.int64, device=q.device)
+    seed = torch.zeros((), dtype=torch.int64, device=q.device)
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+        _to_bhsd(do.to(q.dtype), Hq).contiguous(), _to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq),
+        _to_bhsd(out.to(q.dtype), Hq).contiguous(), lse.float().contiguous(), empty, empty, Sq, Sk, 0.0, causal, seed, seed,
+        scale=scale)
+    dq, dk, dv = dq.permute(0, 2, 1, 3).float(), dk.permute(0, 2, 1, 3).float(), dv.permute(0, 2, 1, 3).float()
+    g = Hq // Hkv
+    if g > 1:
+        dk = dk.reshape(B, Sk, Hkv, g, -1).sum(3)
+        dv = dv.reshape(B, Sk, Hkv, g, -1).sum(3)
+    return dq, dk, dv
+
+
+def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor], causal_diag: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Partial attention of ``q[B,Sq,Hq,D]`` against ``k,v[B,Sk,Hkv,*]``: fp32 ``out[B,Sq,Hq,Dv]`` and
-    ``lse[B,Hq,Sq]`` (``-inf`` for rows that see no key)."""
+    ``lse[B,Hq,Sq]`` (``-inf`` for rows that see no key). ``causal_diag`` says that ``mask`` is exactly the
+    causal mask of equal positions (the diagonal block without a sliding window)."""
+    global _LIB_BLOCKS_BROKEN
+    if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
+        try:
+            return _lib_block_fwd(q, k, v, scale, causal_diag)
+        except (RuntimeError, NotImplementedError):
+            _LIB_BLOCKS_BROKEN = True  # this build has no flash kernel for the device: keep to the math path
     Hq = q.shape[2]
     qf = q.float().permute(0, 2, 1, 3)
     kf = _expand_kv(k, Hq).float().permute(0, 2, 1, 3)
@@ -63,8 +110,14 @@ def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor]) -> Tuple[torc
     return out, lse
 
 
-def block_bwd(do, q, k, v, out, lse, scale: float, mask: Optional[torch.Tensor]):
+def block_bwd(do, q, k, v, out, lse, scale: float, mask: Optional[torch.Tensor], causal_diag: bool = False):
     """Gradients of one partial given the *global* ``out``/``lse`` (flash-attention backward math)."""
+    global _LIB_BLOCKS_BROKEN
+    if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
+        try:
+            return _lib_block_bwd(do, q, k, v, out, lse, scale, causal_diag)
+        except (RuntimeError, NotImplementedError):
+            _LIB_BLOCKS_BROKEN = True
     Hq, Hkv = q.shape[2], k.shape[2]
     g = Hq // Hkv
     qf = q.float().permute(0, 2, 1, 3)
@@ -240,7 +293,8 @@ class _RingAttention(torch.autograd.Function):
                 k_halves, v_halves = (k[:, :block], k[:, block:]), (v[:, :block], v[:, block:])
                 for qi, ki, rel, qb, kb in _pairs(cp, rank, src, block, window_left):
                     mask = None if rel == "full" else block_mask(_positions(qb, block, dev), _positions(kb, block, dev), window_left)
-                    o_p, lse_p = block_fwd(q_halves[qi], k_halves[ki], v_halves[ki], scale, mask)
+                    o_p, lse_p = block_fwd(q_halves[qi], k_halves[ki], v_halves[ki], scale, mask,
+                                           causal_diag=(rel == "mask" and window_left is None and qb == kb))
                     outs[qi], lses[qi] = merge_partial(outs[qi], lses[qi], o_p, lse_p)
             ring.end_step(i)
         ring.finish()
@@ -290,7 +344,8 @@ class _RingAttention(torch.autograd.Function):
                 dk_h, dv_h = halves(dk), halves(dv)
                 for qi, ki, rel, qb, kb in _pairs(cp, rank, src, block, window_left):
                     mask = None if rel == "full" else block_mask(_positions(qb, block, dev), _positions(kb, block, dev), window_left)
-                    dq_p, dk_p, dv_p = block_bwd(do_h[qi], q_h[qi], k_h[ki], v_h[ki], out_h[qi], lse_h[qi], scale, mask)
+                    dq_p, dk_p, dv_p = block_bwd(do_h[qi], q_h[qi], k_h[ki], v_h[ki], out_h[qi], lse_h[qi], scale, mask,
+                                                 causal_diag=(rel == "mask" and window_left is None and qb == kb))
                     dq[qi] += dq_p
                     dk_h[ki].add_(dk_p)
                     dv_h[ki].add_(dv_p)

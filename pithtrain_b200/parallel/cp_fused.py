@@ -111,8 +111,9 @@ class PayloadExchange:
             self._wait(READY + src, 1, epoch, st)
             base = self.buf.peer_ptrs[src] + (epoch & 1) * self.slot_bytes
             for j, t in enumerate(out):
-                # a few dozen CTAs saturate the link and leave the SMs to the attention kernels
-                self._copy(t.data_ptr(), base + self.offsets[j], self._nbytes(j), st, max_ctas=32)
+                # a bounded number of CTAs (eight loads in flight per thread) covers the link and leaves
+                # most SMs to the attention kernels
+                self._copy(t.data_ptr(), base + self.offsets[j], self._nbytes(j), st, max_ctas=64)
                 t.record_stream(self.side)
         ev = torch.cuda.Event()
         ev.record(self.side)

@@ -216,3 +216,32 @@ def test_route_sort_device_side_count(n, k, E, valid):
     _native.check_status()
     assert torch.equal(offs.cpu(), offs_r) and torch.equal(ros.cpu(), ros_r)
     assert torch.equal(sor.cpu(), sor_r)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_ring_blocks_library_vs_math(causal):
+    """The flash-kernel block path of ring attention (with a *global* lse in the backward) equals the fp32 math."""
+    from pithtrain_b200.ops import ring_attention as R
+
+    torch.manual_seed(11)
+    B, S, Hq, Hkv, D = 2, 256, 8, 2, 64
+    q, k, v = bf(B, S, Hq, D), bf(B, S, Hkv, D), bf(B, S, Hkv, D)
+    do = bf(B, S, Hq, D)
+    pos = torch.arange(S, device="cuda")
+    mask = R.block_mask(pos, pos, None) if causal else None
+    outs = []
+    for lib in (True, False):
+        R.USE_LIBRARY_BLOCKS = lib
+        try:
+            o, lse = R.block_fwd(q, k, v, D ** -0.5, mask, causal_diag=causal)
+            # a larger global lse, as when other blocks contributed too
+            lse_g = lse + 0.3
+            o_g = o * torch.exp(lse - lse_g).permute(0, 2, 1).unsqueeze(-1)
+            grads = R.block_bwd(do, q, k, v, o_g, lse_g, D ** -0.5, mask, causal_diag=causal)
+            outs.append((o, lse) + tuple(grads))
+        finally:
+            R.USE_LIBRARY_BLOCKS = True
+    assert not R._LIB_BLOCKS_BROKEN, "the library flash kernel was not usable on this device"
+    for a, b in zip(*outs):
+        assert a.shape == b.shape
+        assert calc_diff(a.float(), b.float()) < 2e-4
