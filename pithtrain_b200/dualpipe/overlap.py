@@ -2,10 +2,14 @@
 
 The forward of a micro-batch through one model chunk and the backward of another micro-batch
 through the other chunk are written as two coroutines that yield at every stage boundary; the
-driver alternates between them. Each side launches its expert exchange (stages 2 and 4) on the
-communication stream and yields, so the other side's compute runs while the exchange is in
-flight, and the expert weight-gradient GEMMs of the backward side are split off (stage 3 "W") to
-fill the time the backward dispatch-gradient exchange takes. The reference hand-unrolls the same
+driver alternates between them. Both sides are cut into four segments per layer so that every
+expert exchange (stages 2 and 4, on the communication stream) is in flight under a compute segment
+of the other side:
+
+    backward: [B5, launch B4] [wait B4, B3 dgrad, launch B2] [B3 wgrad        ] [wait B2, B1 attention]
+    forward :   [F1 attention, launch F2] [wait F2, F3 experts, launch F4] [ -- ] [wait F4, F5]
+
+i.e. on the compute stream: B5, F1 (covers B4), B3 (covers F2), F3 (covers B2), W (covers F4), B1, F5. The reference hand-unrolls the same
 idea for equal layer counts plus special cases (pithtrain/dualpipe/overlap.py:50-331); coroutines
 cover unequal layer counts and dense layers without special cases.
 """
@@ -47,21 +51,24 @@ def forward_coroutine(ctx: ExecutionCtx, module, inputs, rec: ChunkRecord, cu_se
     rec.rotary = rotary
     for layer, lrec in zip(module.layers.values(), rec.layers):
         lrec.merged_prev = False
+        # segment 1: attention + router, then the dispatch goes out on the communication stream
         tokens, residual, routing = stage1_f(layer, lrec, hidden, rotary, cu_seqlens)
         weights = routing.topk_weight if routing is not None else None
-        yield
         region = stage2_f(ctx, layer, lrec, tokens, routing)
+        yield
+        # segment 2: experts, then the combine goes out
         if region is not None:
-            yield
             region.wait()
             tokens, weights = lrec.s2.outputs
         outs = stage3_f(layer, lrec, routing, tokens, weights)
-        yield
         region = stage4_f(ctx, layer, lrec, outs, routing)
+        yield
+        # segment 3: nothing to compute here; the other side's weight gradients cover the combine
         if region is not None:
             yield
             region.wait()
             (outs,) = lrec.s4.outputs
+        # segment 4: residual add
         hidden = stage5_f(layer, lrec, outs, residual, routing)
         yield
     if module.stage_index == module.stage_count - 1:
@@ -80,13 +87,15 @@ def backward_coroutine(ctx: ExecutionCtx, module, rec: ChunkRecord, output_grad,
         d_hidden = output_grad
     layers = list(module.layers.values())
     for layer, lrec in zip(reversed(layers), reversed(rec.layers)):
+        # segment 1: residual split, then the combine-gradient exchange goes out
         d_outs, d_residual = stage5_b(layer, lrec, (d_hidden,))
-        yield
+        region = None
         if lrec.s4.live:
             (d_outs,), region = stage4_b(ctx, layer, lrec, (d_outs,))
-            yield
+        yield
+        # segment 2: expert input gradients (weight gradients split off), then the dispatch-gradient exchange
+        if region is not None:
             region.wait()
-        # dgrad now, expert wgrad later (local deferral, independent of the chunk-level store)
         local: List[Callable] = []
         defer = lrec.is_moe and not WeightGradStore.enabled
         if defer:
@@ -94,17 +103,18 @@ def backward_coroutine(ctx: ExecutionCtx, module, rec: ChunkRecord, output_grad,
         d_tokens, d_weights = stage3_b(layer, lrec, (d_outs,), defer_wgrad=defer)
         if defer:
             WeightGradStore.cache = saved
-        yield
         region = None
         if lrec.s2.live:
             (d_tokens, d_weights), region = stage2_b(ctx, layer, lrec, (d_tokens, d_weights))
-            yield
+        yield
+        # segment 3: the expert weight gradients fill the time both exchanges are in flight
         if local:
             with nvtx_range("layer%02d.stage3_w" % layer.idx), torch.no_grad():
                 for fn in local:
                     fn()
             local.clear()
-            yield
+        yield
+        # segment 4: attention backward
         if region is not None:
             region.wait()
         (d_hidden,) = stage1_b(layer, lrec, (d_tokens, d_residual, d_weights))
