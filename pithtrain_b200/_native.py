@@ -74,7 +74,7 @@ SIGS = {
     "pt_sumsq_grid": "",
     "pt_sumsq": "PILPP",
     "pt_adamw": "PIPIPPLPFFFFFFFP",
-    "pt_muon_momentum": "PIPIPLFP",
+    "pt_muon_momentum": "PIPIPLFPP",
     "pt_symm_malloc": "PL",
     "pt_symm_free": "P",
     "pt_ipc_export": "PP",

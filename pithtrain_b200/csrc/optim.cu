@@ -77,13 +77,15 @@ adamw_kernel(TP* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m
 template <typename TG, typename TB>
 __global__ void __launch_bounds__(256)
 muon_momentum_kernel(const TG* __restrict__ g, TB* __restrict__ buf, __nv_bfloat16* __restrict__ upd,
-                     long long nvec, float beta) {
+                     long long nvec, float beta, const float* __restrict__ grad_scale) {
+  const float gs = grad_scale ? *grad_scale : 1.f;  // deferred 1/num_tokens and clip coefficient
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
     float gf[8], bf[8], uf[8];
     load_as_float8<TG>(g + i * 8, gf);
     load_as_float8<TB>(buf + i * 8, bf);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
+      gf[e] *= gs;
       bf[e] = beta * bf[e] + (1.f - beta) * gf[e];
       uf[e] = (1.f - beta) * gf[e] + beta * bf[e];
     }
@@ -116,13 +118,13 @@ static inline int flat_grid(long long nvec) {
 }
 
 PT_API int pt_muon_momentum(const void* g, int g_fp32, void* buf, int buf_fp32, void* upd, long long numel,
-                            float beta, void* stream_) {
+                            float beta, const float* grad_scale, void* stream_) {
   cudaStream_t st = (cudaStream_t)stream_;
   if (numel <= 0) return 0;
   if (numel % 8 != 0) return -1;
   long long nvec = numel / 8;
   int grid = flat_grid(nvec);
-#define LAUNCH(TG, TB) muon_momentum_kernel<TG, TB><<<grid, 256, 0, st>>>((const TG*)g, (TB*)buf, (__nv_bfloat16*)upd, nvec, beta)
+#define LAUNCH(TG, TB) muon_momentum_kernel<TG, TB><<<grid, 256, 0, st>>>((const TG*)g, (TB*)buf, (__nv_bfloat16*)upd, nvec, beta, grad_scale)
   if (g_fp32 && buf_fp32) LAUNCH(float, float);
   else if (g_fp32) LAUNCH(float, __nv_bfloat16);
   else if (buf_fp32) LAUNCH(__nv_bfloat16, float);

@@ -33,6 +33,12 @@ def _grad_of(p: torch.Tensor) -> Optional[torch.Tensor]:
     return g if g is not None else p.grad
 
 
+def _grad_scale_of(p: torch.Tensor) -> Optional[torch.Tensor]:
+    """Pending factor on ``p``'s accumulated gradient (a device scalar kept by its flat shard group)."""
+    grp = getattr(p, "_shard_group", None)
+    return getattr(grp, "grad_scale", None) if grp is not None else None
+
+
 def _owned(p: torch.Tensor) -> bool:
     grp = getattr(p, "_shard_group", None)
     return True if grp is None else grp.is_owned(p)
@@ -106,10 +112,11 @@ def orthogonalized_updates(params: List[torch.Tensor], updates: List[torch.Tenso
 class _Unit:
     """Contiguous storage that Muon processes in one go."""
 
-    __slots__ = ("w", "g", "params", "key")
+    __slots__ = ("w", "g", "params", "key", "gscale")
 
     def __init__(self, w, g, params, key):
         self.w, self.g, self.params, self.key = w, g, params, key
+        self.gscale = _grad_scale_of(params[0])
 
 
 class Muon(torch.optim.Optimizer):
@@ -194,17 +201,17 @@ class Muon(torch.optim.Optimizer):
                 chunk = max(1, self.max_chunk_elems // per)
                 for s in range(0, u.w.shape[0], chunk):
                     sl = slice(s, min(s + chunk, u.w.shape[0]))
-                    work.append((u.w[sl], u.g[sl], st3[sl]))
+                    work.append((u.w[sl], u.g[sl], st3[sl], u.gscale))
             if not work:
                 continue
             if self.offload_state and work[0][0].is_cuda:
                 self._run_offloaded(work, beta, lr, wd)
             else:
-                for w, g, st in work:
-                    self._update_chunk(w, g, st, beta, lr, wd)
+                for w, g, st, gs in work:
+                    self._update_chunk(w, g, st, beta, lr, wd, gs)
         return loss
 
-    def _update_chunk(self, w, g, buf, beta, lr, wd) -> None:
+    def _update_chunk(self, w, g, buf, beta, lr, wd, gscale=None) -> None:
         """``buf`` is on the same device as ``w`` here."""
         n, m = w.shape[-2], w.shape[-1]
         native = (w.is_cuda and w.dtype == torch.bfloat16 and w.is_contiguous() and g.is_contiguous()
@@ -215,10 +222,10 @@ class Muon(torch.optim.Optimizer):
             upd = torch.empty(w.shape, dtype=torch.bfloat16, device=w.device)
             rc = L.pt_muon_momentum(g.data_ptr(), int(g.dtype == torch.float32), buf.data_ptr(),
                                     int(buf.dtype == torch.float32), upd.data_ptr(), w.numel(), float(beta),
-                                    _native.stream_ptr())
+                                    None if gscale is None else gscale.data_ptr(), _native.stream_ptr())
             _native.check(rc, "pt_muon_momentum")
         else:
-            g32 = g.float()
+            g32 = g.float() if gscale is None else g.float() * gscale.to(g.device)
             b32 = buf.float().lerp_(g32, 1 - beta)
             buf.copy_(b32)
             upd = g32.lerp(b32, beta)
@@ -239,7 +246,7 @@ class Muon(torch.optim.Optimizer):
         if self._streams is None:
             self._streams = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
         h2d, d2h = self._streams
-        max_elems = max(w.numel() for w, _, _ in work)
+        max_elems = max(item[0].numel() for item in work)
         if not self._stage or self._stage[0].numel() < max_elems:
             self._stage = [torch.empty(max_elems, dtype=self.momentum_dtype, device=dev) for _ in range(3)]
         comp = torch.cuda.current_stream(dev)
@@ -250,7 +257,7 @@ class Muon(torch.optim.Optimizer):
             if i >= len(work):
                 return
             k = i % 3
-            w, _, st = work[i]
+            w, _, st = work[i][:3]
             with torch.cuda.stream(h2d):
                 if free_ev[k] is not None:
                     h2d.wait_event(free_ev[k])
@@ -262,10 +269,10 @@ class Muon(torch.optim.Optimizer):
 
         prefetch(0)
         prefetch(1)
-        for i, (w, g, st) in enumerate(work):
+        for i, (w, g, st, gs) in enumerate(work):
             view, ev = loaded.pop(i)
             comp.wait_event(ev)
-            self._update_chunk(w, g, view, beta, lr, wd)
+            self._update_chunk(w, g, view, beta, lr, wd, gs)
             done = torch.cuda.Event()
             done.record(comp)
             with torch.cuda.stream(d2h):
@@ -305,6 +312,7 @@ class AdamW(torch.optim.Optimizer):
                     st["exp_avg_sq"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
                 st["step"] += 1
                 t = float(st["step"])
+                gs = _grad_scale_of(p)
                 m, v = st["exp_avg"], st["exp_avg_sq"]
                 bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
                 if (p.is_cuda and p.is_contiguous() and g.is_contiguous() and p.numel() % 8 == 0
@@ -312,11 +320,11 @@ class AdamW(torch.optim.Optimizer):
                         and p.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0):
                     rc = _native.lib().pt_adamw(p.data_ptr(), int(p.dtype == torch.float32), g.data_ptr(),
                                                 int(g.dtype == torch.float32), m.data_ptr(), v.data_ptr(), p.numel(),
-                                                None, float(lr), float(b1), float(b2), float(eps), float(wd),
+                                                None if gs is None else gs.data_ptr(), float(lr), float(b1), float(b2), float(eps), float(wd),
                                                 float(bc1), float(bc2), _native.stream_ptr())
                     _native.check(rc, "pt_adamw")
                     continue
-                g32 = g.float()
+                g32 = g.float() if gs is None else g.float() * gs.to(g.device)
                 m.lerp_(g32, 1 - b1)
                 v.mul_(b2).addcmul_(g32, g32, value=1 - b2)
                 denom = (v / bc2).sqrt_().add_(eps)

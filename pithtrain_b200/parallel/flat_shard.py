@@ -88,6 +88,8 @@ class FlatShardGroup:
         self.group, self.group_size, self.group_rank = group, group_size, group_rank
         self.replica_group, self.replica_size = replica_group, replica_size
         self.grad_divisor = 1
+        self.defer_grad_scale = True
+        self.grad_scale: Optional[torch.Tensor] = None  # pending factor on the accumulated gradients (device, [1])
         self.units = collect_units(named_params, fusions)
         self.named_params = list(named_params)
         if not self.units:
@@ -177,7 +179,17 @@ class FlatShardGroup:
                 p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                 p.grad = None
 
+    def apply_clip(self, coef: torch.Tensor) -> None:
+        """Scale the owned gradients by the clip coefficient (folded into ``grad_scale`` when deferred)."""
+        if self.flat_grad is None:
+            return
+        if self.grad_scale is not None:
+            self.grad_scale = self.grad_scale * coef.to(torch.float32).reshape(1)
+        else:
+            self.my_slice(self.flat_grad).mul_(coef.to(self.flat_grad.dtype))
+
     def zero_grad(self) -> None:
+        self.grad_scale = None
         if self.flat_grad is not None:
             if self.comm is not None:
                 self.comm.before_zero_grad()  # owners may still be reading this rank's gradients
@@ -194,8 +206,16 @@ class FlatShardGroup:
         pithtrain/tasks/pretrain_lm.py:393-396 together with the dp×cp expert mesh of
         pithtrain/modules/training.py:364-370.)
         """
-        if self.flat_grad is not None:
-            self.flat_grad.mul_(scale / self.grad_divisor if self.grad_divisor != 1 else scale)
+        if self.flat_grad is None:
+            return
+        scale = scale / self.grad_divisor if self.grad_divisor != 1 else scale
+        if self.flat_grad.is_cuda and self.defer_grad_scale:
+            # no pass over the gradients: the factor travels to the optimizer kernels as a device scalar
+            # (grad_scale) and the norm is corrected by its square
+            s = torch.as_tensor(scale, dtype=torch.float32, device=self.flat_grad.device).reshape(1)
+            self.grad_scale = s if self.grad_scale is None else self.grad_scale * s
+        else:
+            self.flat_grad.mul_(scale)
 
     def reduce_grads(self) -> None:
         """Average gradients over the shard group; afterwards only this rank's region is meaningful."""
@@ -222,6 +242,13 @@ class FlatShardGroup:
             mine.div_(self.replica_size)
 
     def owned_grad_sumsq(self) -> torch.Tensor:
+        """Sum of squares of this rank's reduced gradients (with any pending scale applied)."""
+        raw = self._owned_grad_sumsq_raw()
+        if self.grad_scale is not None:
+            raw = raw.to(self.grad_scale.device) * (self.grad_scale[0] * self.grad_scale[0])
+        return raw
+
+    def _owned_grad_sumsq_raw(self) -> torch.Tensor:
         if self.flat_grad is None:
             return torch.zeros((), dtype=torch.float32)
         if self._fused_sumsq is not None:

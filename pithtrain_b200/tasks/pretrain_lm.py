@@ -116,8 +116,7 @@ def clip_grad_norm_(model: Optional[nn.Module] = None, max_norm: float = 1.0, no
     coef = (max_norm / total).clamp(max=1.0)
     if groups:
         for g in groups:
-            if g.flat_grad is not None:
-                g.my_slice(g.flat_grad).mul_(coef.to(g.flat_grad.dtype))
+            g.apply_clip(coef)
     else:
         for p in model.parameters():
             if p.grad is not None:
