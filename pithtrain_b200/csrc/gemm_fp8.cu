@@ -9,10 +9,11 @@
 // the tensor cores already work on the next k-block in the other buffer — two-level accumulation
 // with the promotion running concurrently with the MMAs instead of stalling them.
 //
-//   warp 0      TMA producer   : A and B k-blocks (128 rows x 128 bytes, 128B swizzle) into a ring
-//   warp 1      MMA issuer     : 4 x (M128 N128 K32) per k-block, commit -> smem stage free, TMEM full
+//   warp 0      TMA producer   : A (128 rows) and B (256 rows) k-blocks of 128 bytes, 128B swizzle, into a ring
+//   warp 1      MMA issuer     : 4 x (M128 N256 K32) per k-block, commit -> smem stage free, TMEM full
 //   warps 2..9  promotion + epilogue: tcgen05.ld, scaled FMA, bf16 store (TMA store or direct rows);
-//               two warps per TMEM lane quarter, each owning one 64-column half of the tile
+//               two warps per TMEM lane quarter, each owning one 128-column half of the tile (= one
+//               128-wide weight scale block)
 //
 // Modes: dense, and M-grouped (expert GEMMs: rows grouped by a device-side offsets array, group g
 // uses weight rows [g*b_group_rows, ...)). Takes the role of DeepGEMM's fp8_gemm_nt and
@@ -24,15 +25,16 @@
 namespace pt {
 namespace f8 {
 
-constexpr int BM = 128, BN = 128, BK = 128;  // BK bytes = one 128-byte swizzle row = one scale block
+constexpr int BM = 128, BN = 256, BK = 128;  // BK bytes = one 128-byte swizzle row = one scale block
 constexpr int UMMA_K = 32;
-constexpr int TILE_BYTES = BM * BK;  // 16 KB per operand per stage
-constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-constexpr int STAGES = 5;
+constexpr int TILE_BYTES = BM * BK;    // A: 16 KB per stage
+constexpr int B_TILE_BYTES = BN * BK;  // B: 32 KB per stage
+constexpr int STAGE_BYTES = TILE_BYTES + B_TILE_BYTES;
+constexpr int STAGES = 4;
 constexpr int EPI_WARPS = 8;  // two per TMEM lane quarter: each folds one 64-column half of the tile
 constexpr int STAGING_BYTES = EPI_WARPS * 4096;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
-constexpr int NBUF = 4;  // k-block accumulators in flight: hides the commit -> tcgen05.ld -> release round trip
+constexpr int NBUF = 2;  // k-block accumulators in flight
 constexpr uint32_t TMEM_COLS = NBUF * BN;  // 512: the whole tensor memory of the SM
 constexpr uint32_t IDESC = make_idesc(0, 0, BM, BN, false, false);
 
@@ -145,7 +147,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           mbar_expect_tx(&full[s], STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
           tma_load_2d(sa, &tmA, &full[s], kb * BK, ti.am);
-          tma_load_2d(sa + TILE_BYTES, &tmB, &full[s], kb * BK, ti.bn);
+          tma_load_2d(sa + TILE_BYTES, &tmB, &full[s], kb * BK, ti.bn);  // 256 rows x 128 bytes
         }
       }
       if (*abort_flag) {
@@ -197,7 +199,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else {
     const int q = warp & 3;            // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;  // which 64 columns of the tile this warp folds
+    const int half = (warp - 2) >> 2;  // which half (128 columns) of the tile this warp folds
     constexpr int HC = BN / 2;
     Sched sch(args);
     Tile ti;
@@ -208,7 +210,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int row = ti.row0 + q * 32 + lane;
       const bool rvalid = row < ti.row_end;
       const float* sa_p = args.sa + row;
-      const float* sb_p = args.sb + ((long long)ti.grp * nblocks + ti.nt) * num_kb;
+      const int nb_idx = min(ti.nt * (BN / 128) + half, nblocks - 1);  // the 128-wide weight block of this half
+      const float* sb_p = args.sb + ((long long)ti.grp * nblocks + nb_idx) * num_kb;
       float acc[HC];
 #pragma unroll
       for (int i = 0; i < HC; ++i) acc[i] = 0.f;
@@ -224,18 +227,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * HC;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(taddr, r0);
-        tmem_ld_32x32(taddr + 32, r1);
-        tmem_ld_wait();
-        // the partial is in registers: hand the TMEM buffer back before doing the arithmetic
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), sc, acc[j]);
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (c == HC / 32 - 1) {
+            // the whole partial has left TMEM: hand the buffer back before the last arithmetic
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(r1[j]), sc, acc[32 + j]);
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c * 32 + j]);
+        }
       }
       if (!ok) break;
       const bool full_tile = (args.mode == 0) ? (ti.row0 + BM <= args.M) : (ti.row0 + BM <= ti.row_end);
@@ -243,23 +248,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (col0 >= args.N) continue;  // uniform across the warp
       if (args.use_tma_store && full_tile) {
         used_tma = true;
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
-        uint8_t* rowp = st + lane * 128;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 v;
-          v.x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
-          v.y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
-          v.z = pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]);
-          v.w = pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]);
-          *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmD, st, col0, ti.row0 + q * 32);
-          tma_store_commit();
+        for (int cc = 0; cc < HC / 64; ++cc) {
+          if (col0 + cc * 64 < args.N) {
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+            uint8_t* rowp = st + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(acc[cc * 64 + 8 * j + 0], acc[cc * 64 + 8 * j + 1]);
+              v.y = pack_bf16x2(acc[cc * 64 + 8 * j + 2], acc[cc * 64 + 8 * j + 3]);
+              v.z = pack_bf16x2(acc[cc * 64 + 8 * j + 4], acc[cc * 64 + 8 * j + 5]);
+              v.w = pack_bf16x2(acc[cc * 64 + 8 * j + 6], acc[cc * 64 + 8 * j + 7]);
+              *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, st, col0 + cc * 64, ti.row0 + q * 32);
+              tma_store_commit();
+            }
+          }
         }
       } else if (rvalid) {
         __nv_bfloat16* p = args.D + (long long)row * args.ldd + col0;

@@ -46,7 +46,7 @@ def block_mask(q_pos: torch.Tensor, k_pos: torch.Tensor, window_left: Optional[i
     return m
 
 
-# Blocks that need no explicit mask (fully visible, or the causal diagonal block) go to the library flash
+# Blocks that need no explicit mask (fully visible, or the causal diagonal block) go to the library (cuDNN) flash
 # kernel on GPUs, which returns the log-sum-exp the merge needs; everything else uses the fp32 math below.
 USE_LIBRARY_BLOCKS = True
 _LIB_BLOCKS_BROKEN = False
@@ -61,23 +61,32 @@ def _to_bhsd(t: torch.Tensor, Hq: int) -> torch.Tensor:
     return _expand_kv(t, Hq).permute(0, 2, 1, 3)
 
 
+_LIB_BLOCKS_ERROR = ""
+
+
 def _lib_block_fwd(q, k, v, scale: float, causal: bool):
+    """cuDNN flash forward of one block; returns fp32 ``out[B,S,H,D]`` and ``lse[B,H,S]``."""
     Hq = q.shape[2]
-    res = torch.ops.aten._scaled_dot_product_flash_attention(_to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq), 0.0, causal,
-                                                             False, scale=scale)
+    res = torch.ops.aten._scaled_dot_product_cudnn_attention(_to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq), None, True,
+                                                             0.0, causal, False, scale=scale)
     out, lse = res[0], res[1]
-    return out.permute(0, 2, 1, 3).float(), lse.float()
+    B, H, S = out.shape[0], out.shape[1], out.shape[2]
+    return out.permute(0, 2, 1, 3).float(), lse.reshape(B, H, S).float()
 
 
 def _lib_block_bwd(do, q, k, v, out, lse, scale: float, causal: bool):
+    """cuDNN flash backward of one block against the *global* ``out``/``lse``."""
     Hq, Hkv = q.shape[2], k.shape[2]
     B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
-    empty = torch.empty(0, dtype=torch.int64, device=q.device)
-    seed = torch.zeros((), dtype=torch.int64, device=q.device)
-    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-        _to_bhsd(do.to(q.dtype), Hq).contiguous(), _to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq),
-        _to_bhsd(out.to(q.dtype), Hq).contiguous(), lse.float().contiguous(), empty, empty, Sq, Sk, 0.0, causal, seed, seed,
-        scale=scale)
+    dev = q.device
+    empty = torch.empty(0, dtype=torch.int64, device=dev)
+    seed = torch.zeros((), dtype=torch.int64, device=dev)
+    qb, kb, vb = _to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq)
+    ob = _to_bhsd(out.to(q.dtype), Hq)
+    dob = _to_bhsd(do.to(q.dtype), Hq)
+    lse4 = lse.float().reshape(B, Hq, Sq, 1).contiguous()
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+        dob, qb, kb, vb, ob, lse4, seed, seed, None, empty, empty, Sq, Sk, 0.0, causal, scale=scale)
     dq, dk, dv = dq.permute(0, 2, 1, 3).float(), dk.permute(0, 2, 1, 3).float(), dv.permute(0, 2, 1, 3).float()
     g = Hq // Hkv
     if g > 1:
@@ -94,8 +103,9 @@ def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor], causal_diag: 
     if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
         try:
             return _lib_block_fwd(q, k, v, scale, causal_diag)
-        except (RuntimeError, NotImplementedError):
-            _LIB_BLOCKS_BROKEN = True  # this build has no flash kernel for the device: keep to the math path
+        except (RuntimeError, NotImplementedError, TypeError) as e:
+            global _LIB_BLOCKS_ERROR
+            _LIB_BLOCKS_BROKEN, _LIB_BLOCKS_ERROR = True, repr(e)  # no usable library kernel: keep to the math path
     Hq = q.shape[2]
     qf = q.float().permute(0, 2, 1, 3)
     kf = _expand_kv(k, Hq).float().permute(0, 2, 1, 3)
@@ -116,8 +126,9 @@ def block_bwd(do, q, k, v, out, lse, scale: float, mask: Optional[torch.Tensor],
     if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
         try:
             return _lib_block_bwd(do, q, k, v, out, lse, scale, causal_diag)
-        except (RuntimeError, NotImplementedError):
-            _LIB_BLOCKS_BROKEN = True
+        except (RuntimeError, NotImplementedError, TypeError) as e:
+            global _LIB_BLOCKS_ERROR
+            _LIB_BLOCKS_BROKEN, _LIB_BLOCKS_ERROR = True, repr(e)
     Hq, Hkv = q.shape[2], k.shape[2]
     g = Hq // Hkv
     qf = q.float().permute(0, 2, 1, 3)

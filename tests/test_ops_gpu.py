@@ -241,7 +241,7 @@ def test_ring_blocks_library_vs_math(causal):
             outs.append((o, lse) + tuple(grads))
         finally:
             R.USE_LIBRARY_BLOCKS = True
-    assert not R._LIB_BLOCKS_BROKEN, "the library flash kernel was not usable on this device"
+    assert not R._LIB_BLOCKS_BROKEN, "the library flash kernel was not usable on this device: " + R._LIB_BLOCKS_ERROR
     for a, b in zip(*outs):
         assert a.shape == b.shape
         assert calc_diff(a.float(), b.float()) < 2e-4
