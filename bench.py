@@ -121,6 +121,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (result is marked invalid)")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--optimizer", default="muon")
+    ap.add_argument("--resident-state-gb", type=float, default=22.0,
+                    help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
     args = ap.parse_args()
     if args.impl == "reference":
@@ -159,6 +161,7 @@ def main() -> int:
     t.grad_dtype = "bf16"
     t.muon_momentum_dtype = "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
+    t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
     t.num_hidden_layers_override = args.layers
 
     setup_logging(cfg)
@@ -244,7 +247,7 @@ def main() -> int:
                 "global_batch": t.global_batch_size, "global_batch_tokens": tokens_per_step, "seq_len": SEQ_LEN,
                 "micro_batch": 1, "parallelism": f"pp{pp}xcp{cp}xep{ep}xdp{distributed.dp_size}",
                 "optimizer": "Muon (2-D/expert weights) + AdamW (rest), grad clip 1.0" if args.optimizer == "muon" else "AdamW",
-                "grad_accumulators": t.grad_dtype, "muon_momentum": t.muon_momentum_dtype + (", pinned host memory (streamed each step)" if t.offload_optimizer_state else ""),
+                "grad_accumulators": t.grad_dtype, "muon_momentum": t.muon_momentum_dtype + (f", {t.optimizer_device_state_gb:.0f} GiB resident + the rest in pinned host memory (streamed each step)" if t.offload_optimizer_state else ""),
                 "routing": "natural (seeded random-init gate)", "ep_transport": args.ep_backend,
                 "l2": "inputs larger than L2: every step streams >10 GB of parameters and activations, no explicit flush",
             },

@@ -124,11 +124,15 @@ class Muon(torch.optim.Optimizer):
 
     def __init__(self, params, lr: float = 0.02, momentum: float = 0.95, weight_decay: float = 0.1,
                  momentum_dtype: torch.dtype = torch.float32, offload_state: bool = False,
-                 max_chunk_elems: int = 1 << 28):
+                 max_chunk_elems: int = 1 << 28, device_state_budget: int = 0):
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.momentum_dtype = momentum_dtype
         self.offload_state = offload_state
+        # with offload_state: bytes of momentum that may stay on the device anyway (largest use of spare HBM:
+        # every byte kept resident is a byte that does not cross PCIe twice per step)
+        self.device_state_budget = int(device_state_budget)
+        self._device_state_bytes = 0
         self.max_chunk_elems = max_chunk_elems
         self._unit_state: Dict[int, torch.Tensor] = {}
         self._streams = None
@@ -137,7 +141,10 @@ class Muon(torch.optim.Optimizer):
     # ------------------------------------------------------------------ state
     def _new_state(self, like: torch.Tensor) -> torch.Tensor:
         if self.offload_state and like.is_cuda:
-            return torch.zeros(like.shape, dtype=self.momentum_dtype, device="cpu", pin_memory=True)
+            nbytes = like.numel() * torch.empty((), dtype=self.momentum_dtype).element_size()
+            if self._device_state_bytes + nbytes > self.device_state_budget:
+                return torch.zeros(like.shape, dtype=self.momentum_dtype, device="cpu", pin_memory=True)
+            self._device_state_bytes += nbytes
         return torch.zeros(like.shape, dtype=self.momentum_dtype, device=like.device)
 
     def _units(self, group) -> List[_Unit]:
@@ -205,7 +212,14 @@ class Muon(torch.optim.Optimizer):
             if not work:
                 continue
             if self.offload_state and work[0][0].is_cuda:
-                self._run_offloaded(work, beta, lr, wd)
+                host = [item for item in work if not item[2].is_cuda]
+                resident = [item for item in work if item[2].is_cuda]
+                # host-resident chunks first, so their write-back drains while the resident ones compute
+                if host:
+                    self._run_offloaded(host, beta, lr, wd, tail=resident)
+                else:
+                    for w, g, st, gs in resident:
+                        self._update_chunk(w, g, st, beta, lr, wd, gs)
             else:
                 for w, g, st, gs in work:
                     self._update_chunk(w, g, st, beta, lr, wd, gs)
@@ -240,7 +254,7 @@ class Muon(torch.optim.Optimizer):
             w.mul_(1 - lr * wd)
             w.add_(orth.to(w.dtype), alpha=-lr * scale)
 
-    def _run_offloaded(self, work, beta, lr, wd) -> None:
+    def _run_offloaded(self, work, beta, lr, wd, tail=()) -> None:
         """Stream host-resident momentum chunks through three device staging buffers."""
         dev = work[0][0].device
         if self._streams is None:
@@ -282,6 +296,8 @@ class Muon(torch.optim.Optimizer):
                 fe.record(d2h)
             free_ev[i % 3] = fe
             prefetch(i + 2)
+        for w, g, st, gs in tail:
+            self._update_chunk(w, g, st, beta, lr, wd, gs)
         comp.wait_stream(d2h)
 
 

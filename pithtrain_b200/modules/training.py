@@ -59,7 +59,8 @@ def make_muon_optimizer(cfg: "TrainingCfg", *, weight_decay: float = 0.1) -> tup
         (muon_params if is_muon_param(name, p) else adamw_params).append(p)
     mdt = {"fp32": torch.float32, "bf16": torch.bfloat16}[cfg.muon_momentum_dtype]
     return (Muon(muon_params, lr=cfg.lr, weight_decay=weight_decay, momentum_dtype=mdt,
-                 offload_state=cfg.offload_optimizer_state),
+                 offload_state=cfg.offload_optimizer_state,
+                 device_state_budget=int(cfg.optimizer_device_state_gb * (1 << 30))),
             AdamW(adamw_params, lr=cfg.lr, weight_decay=weight_decay))
 
 
@@ -136,6 +137,8 @@ class TrainingCfg(SlottedDefault):
     """dtype of the flat gradient accumulators (fp32 matches the reference's reduce dtype)."""
     muon_momentum_dtype: Literal["fp32", "bf16"] = "fp32"
     offload_optimizer_state: bool = False
+    optimizer_device_state_gb: float = 0.0
+    """With ``offload_optimizer_state``: GiB of Muon momentum that stay on the device anyway."""
     """Keep Muon momentum in pinned host memory and stream it through the GPU during the step."""
     max_grad_norm: float = 1.0
     num_hidden_layers_override: Optional[int] = None
