@@ -79,14 +79,14 @@ def _lib_block_bwd(do, q, k, v, out, lse, scale: float, causal: bool):
     Hq, Hkv = q.shape[2], k.shape[2]
     B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
     dev = q.device
-    empty = torch.empty(0, dtype=torch.int64, device=dev)
     seed = torch.zeros((), dtype=torch.int64, device=dev)
     qb, kb, vb = _to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq)
     ob = _to_bhsd(out.to(q.dtype), Hq)
     dob = _to_bhsd(do.to(q.dtype), Hq)
     lse4 = lse.float().reshape(B, Hq, Sq, 1).contiguous()
+    # undefined (None) cumulative-length tensors select the dense, non-nested path of the op
     dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
-        dob, qb, kb, vb, ob, lse4, seed, seed, None, empty, empty, Sq, Sk, 0.0, causal, scale=scale)
+        dob, qb, kb, vb, ob, lse4, seed, seed, None, None, None, Sq, Sk, 0.0, causal, scale=scale)
     dq, dk, dv = dq.permute(0, 2, 1, 3).float(), dk.permute(0, 2, 1, 3).float(), dv.permute(0, 2, 1, 3).float()
     g = Hq // Hkv
     if g > 1:
