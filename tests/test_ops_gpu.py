@@ -245,3 +245,23 @@ def test_ring_blocks_library_vs_math(causal):
     for a, b in zip(*outs):
         assert a.shape == b.shape
         assert calc_diff(a.float(), b.float()) < 2e-4
+
+
+def test_bounded_wait_reports_through_status_word():
+    """A wait on a flag that nothing sets gives up after its time limit, records the reason in the status word and
+    leaves the context usable (the host learns of the failure, no kernel spins forever)."""
+    import time
+
+    ctl = torch.zeros(128, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.time()
+    rc = _native.lib().pt_symm_wait(ctl.data_ptr(), 0, 1, 1, _native.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 10.0, waited  # the limit is 2 s
+    with pytest.raises(RuntimeError, match="4|peer|timeout"):
+        _native.check_status()
+    _native.check_status()  # cleared by the read
+    y = bf(64, 64) + 1  # the context still works
+    assert torch.isfinite(y.float()).all()
