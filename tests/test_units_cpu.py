@@ -280,3 +280,19 @@ def test_native_signature_table_matches_sources():
         assert SIGS[name] == sig, (name, SIGS[name], sig)
         found += 1
     assert found >= 30
+
+
+def test_reference_package_name_alias():
+    """Scripts written against the reference's package name import this framework's modules."""
+    from pithtrain.modules.training import make_muon_optimizer, make_wsd_scheduler  # noqa: F401
+    from pithtrain.operators.ring_attention import ring_attention_func
+    from pithtrain.tasks.pretrain_lm import PretrainLMCfg, launch  # noqa: F401
+
+    import pithtrain_b200.ops.ring_attention as impl
+    import pithtrain_b200.tasks.pretrain_lm as impl_task
+
+    assert ring_attention_func is impl.ring_attention_func and PretrainLMCfg is impl_task.PretrainLMCfg
+    import pithtrain.contexts.distributed as ctx_alias
+    import pithtrain_b200.contexts.distributed as ctx_impl
+
+    assert ctx_alias is ctx_impl  # one module object: no duplicated global state
