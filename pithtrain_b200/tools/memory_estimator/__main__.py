@@ -32,6 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--optimizer", choices=["muon", "adamw"], default="muon")
     ap.add_argument("--momentum-dtype", choices=["bf16", "fp32"], default="bf16")
     ap.add_argument("--offload-optimizer-state", action="store_true")
+    ap.add_argument("--resident-state-gb", type=float, default=0.0, help="with offload: GiB of optimizer state kept on the device")
     ap.add_argument("--ep-backend", choices=["fused", "nccl"], default="fused")
     ap.add_argument("--pp-rank", type=int, default=-1, help="-1 = report the worst rank")
     ap.add_argument("--ep-imbalance", type=float, default=1.0)
@@ -48,7 +49,8 @@ def main(argv=None) -> int:
     par = ParallelCfg(pp=a.pp_size, ep=a.ep_size, cp=a.cp_size, dp=total // inner, micro_batch_size=a.micro_batch_size,
                       global_batch_size=a.global_batch_size, sequence_length=a.sequence_length, grad_dtype=a.grad_dtype,
                       optimizer=a.optimizer, momentum_dtype=a.momentum_dtype,
-                      offload_optimizer_state=a.offload_optimizer_state, ep_backend=a.ep_backend)
+                      offload_optimizer_state=a.offload_optimizer_state, resident_state_gb=a.resident_state_gb,
+                      ep_backend=a.ep_backend)
     dims = ModelDims.from_json(a.model)
     ranks = [a.pp_rank] if a.pp_rank >= 0 else list(range(par.pp))
     ests = {r: estimate(dims, par, r, a.ep_imbalance, a.fragmentation, keep_timeline=a.timeline) for r in ranks}

@@ -33,6 +33,7 @@ class ParallelCfg:
     optimizer: str = "muon"  # "muon" (momentum; AdamW for non-matrix params) or "adamw"
     momentum_dtype: str = "bf16"
     offload_optimizer_state: bool = False
+    resident_state_gb: float = 0.0  # with offload: GiB of optimizer state kept on the device anyway
     ep_backend: str = "fused"  # "fused" (symmetric buffers) or "nccl"
     capacity_factor: float = 1.5
 
@@ -216,8 +217,9 @@ def static_memory(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> StaticMemo
         state = mb * (dense_owned - adam_elems + expert_owned) + 8 * adam_elems
     state = int(state)
     if par.offload_optimizer_state:
-        out.optimizer_host = state
-        out.optimizer_device = 3 * 512 * 1024 * 1024  # staging buffers of the host-offloaded optimizer
+        resident = min(state, int(par.resident_state_gb * (1 << 30)))
+        out.optimizer_host = state - resident
+        out.optimizer_device = resident + 3 * 512 * 1024 * 1024  # + staging buffers of the host-offloaded part
     else:
         out.optimizer_device = state
     out.detail = {"dense_param_elems": int(dense), "expert_param_elems": int(expert), "edge_param_elems": int(edge)}
