@@ -43,7 +43,9 @@ def _canonical(name: str) -> str:
 
 
 def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int, overlap: bool = True,
-        device_type: str = "cpu", ep_backend: str = "nccl"):
+        device_type: str = "cpu", ep_backend: str = "nccl", packed: bool = False, forward_only: bool = False):
+    """``packed``: every micro-batch holds two documents (cu_seqlens), attention must not cross the boundary.
+    ``forward_only``: ``step`` under ``no_grad`` with ``return_outputs`` (the inference path) against the oracle."""
     from pithtrain_b200.contexts import distributed
     from pithtrain_b200.dualpipe.dualpipev import DualPipeV
     from pithtrain_b200.dualpipe.comm import set_p2p_tensor_dtype, set_p2p_tensor_shapes
@@ -82,8 +84,11 @@ def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int
             elif "bias" in n or "sinks" in n:
                 p.normal_(0, 0.05)
     ref_loss = 0.0
+    cuts = [torch.tensor([0, 3 + (i % 5), S], dtype=torch.int32, device=dev) for i in range(ids.shape[0])] if packed else None
+    ref_logits = []
     for i in range(ids.shape[0]):
-        logits = full.reference_forward(ids[i:i + 1].to(dev))
+        logits = full.reference_forward(ids[i:i + 1].to(dev), cuts[i] if packed else None)
+        ref_logits.append(logits.detach().float().cpu())
         loss = torch.nn.functional.cross_entropy(logits.view(-1, V).float(), labels[i].to(dev), reduction="sum")
         loss.backward()
         ref_loss += float(loss)
@@ -118,8 +123,23 @@ def run(rank: int, world: int, model_key: str, pp: int, ep: int, num_chunks: int
 
     mine = slice(distributed.ep_rank, None, dp_like)
     my_ids, my_labels = ids[mine].to(dev), labels[mine].to(dev)
+    my_cuts = cuts[distributed.ep_rank::dp_like] if packed else None
+    if forward_only:
+        with torch.no_grad():
+            _, outs = model.step(my_ids if distributed.pp_rank == 0 else None, num_chunks=num_chunks,
+                                 cu_seqlens=my_cuts if distributed.pp_rank == 0 else None, return_outputs=True)
+        if distributed.pp_rank == 0:
+            want = torch.cat(ref_logits[distributed.ep_rank::dp_like], 0)
+            from utilities import calc_diff
+
+            assert outs.shape == want.shape, (outs.shape, want.shape)
+            assert calc_diff(outs.float().cpu(), want) < (1e-6 if dtype == torch.float32 else 1e-3)
+        else:
+            assert outs is None
+        return
     loss, _ = model.step(my_ids if distributed.pp_rank == 0 else None, num_chunks=num_chunks, criterion=criterion,
-                         labels=my_labels if distributed.pp_rank == 0 else None)
+                         labels=my_labels if distributed.pp_rank == 0 else None,
+                         cu_seqlens=my_cuts if distributed.pp_rank == 0 else None)
     total = torch.zeros((), device=dev)
     if loss is not None:
         total += loss.sum()
