@@ -25,7 +25,6 @@ constexpr int BK = 64;  // bf16 elements per k-block = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int EPI_WARPS = 4;
-constexpr int STAGING_BYTES = EPI_WARPS * 2 * 4096;  // two 32x64 bf16 buffers per epilogue warp
 
 enum GemmMode : int { GEMM_DENSE = 0, GEMM_MGROUP = 1, GEMM_KGROUP = 2 };
 
@@ -120,20 +119,25 @@ struct Scheduler {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN, bool A_GATHER>
+// DEEP_EPI trades operand ring depth for epilogue staging: the TMA reduce-add (a read-modify-write in L2) has a
+// long latency, and with two 4 KB slabs per warp only 32 KB per SM are in flight; six slabs per warp keep the
+// gradient accumulation of the short-K expert weight-gradient tiles fed.
+template <int BN, bool A_MN, bool B_MN, bool A_GATHER, bool DEEP_EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const GemmArgs args) {
   constexpr int B_TILE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr int STAGES = DEEP_EPI ? 3 : ((BN == 256) ? 4 : 6);
+  constexpr int NSTG = DEEP_EPI ? ((BN == 256) ? 5 : 6) : 2;  // staging slabs per epilogue warp
+  constexpr int STAGING = EPI_WARPS * NSTG * 4096;
   constexpr uint32_t IDESC = make_idesc(1, 1, BM, BN, A_MN, B_MN);
   constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: power of two
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + STAGING);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -318,6 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     TileInfo ti;
     uint32_t tc = 0;
     bool used_tma = false;
+    uint32_t slab = 0;  // rotation through the staging slabs of this warp (TMA reduce epilogue)
     while (sch.next(ti)) {
       int acc = tc & 1;
       uint32_t aph = (tc >> 1) & 1;
@@ -334,7 +339,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc < BN / 64; ++cc) {
           if (ti.col0 + cc * 64 >= args.N) break;
-          uint8_t* st = staging + (q * 2 + (cc & 1)) * 4096;
+          uint8_t* st = staging + (q * NSTG + (cc & 1)) * 4096;
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
           uint32_t r0[32], r1[32];
@@ -374,8 +379,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc * cols_per < BN; ++cc) {
           if (ti.col0 + cc * cols_per >= args.N) break;
-          uint8_t* st = staging + (q * 2 + (cc & 1)) * 4096;
-          if (lane == 0) tma_store_wait_read<1>();
+          uint8_t* st = staging + (q * NSTG + (slab % NSTG)) * 4096;
+          ++slab;
+          if (lane == 0) tma_store_wait_read<NSTG - 1>();
           __syncwarp();
           uint8_t* rowp = st + lane * 128;
           if (args.out_fp32) {
@@ -464,7 +470,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         // ---- staged: registers -> swizzled smem slab -> coalesced 128-byte row segments in global
         // (read-modify-write when accumulating). Handles ragged rows/columns and both output dtypes.
-        uint8_t* st = staging + q * 2 * 4096;
+        uint8_t* st = staging + q * NSTG * 4096;
         const int cols_per = args.out_fp32 ? 32 : 64;
         const int sub_row = lane >> 3, chunk = lane & 7;
 #pragma unroll 1
@@ -548,16 +554,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <int BN>
+template <int BN, bool DEEP_EPI>
 constexpr int gemm_smem_bytes() {
-  return ((BN == 256) ? 4 : 6) * (A_TILE_BYTES + BN * BK * 2) + STAGING_BYTES + 256 + 1024;
+  return (DEEP_EPI ? 3 : ((BN == 256) ? 4 : 6)) * (A_TILE_BYTES + BN * BK * 2) +
+         EPI_WARPS * (DEEP_EPI ? ((BN == 256) ? 5 : 6) : 2) * 4096 + 256 + 1024;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool A_GATHER = false>
+template <int BN, bool A_MN, bool B_MN, bool A_GATHER = false, bool DEEP_EPI = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
                 const GemmArgs& args, int grid, cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, A_GATHER>;
-  constexpr int smem = gemm_smem_bytes<BN>();
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, A_GATHER, DEEP_EPI>;
+  constexpr int smem = gemm_smem_bytes<BN, DEEP_EPI>();
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -645,6 +652,10 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
                                : launch_gemm<256, false, false, true>(tmA, tmB, tmD, args, grid, stream);
     return b_mn ? launch_gemm<128, false, true, true>(tmA, tmB, tmD, args, grid, stream)
                 : launch_gemm<128, false, false, true>(tmA, tmB, tmD, args, grid, stream);
+  }
+  if (mode == GEMM_KGROUP && tma_reduce && a_mn && b_mn) {
+    return bn == 256 ? launch_gemm<256, true, true, false, true>(tmA, tmB, tmD, args, grid, stream)
+                     : launch_gemm<128, true, true, false, true>(tmA, tmB, tmD, args, grid, stream);
   }
   int key = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (key) {

@@ -82,3 +82,26 @@ def test_fp8_expert_block_close_to_bf16():
             F8.enable(False)
     for a, b in zip(*outs):
         assert calc_diff(a, b) < 1e-2
+
+
+def test_fp8_gradients_feed_muon():
+    """fp8 forward/backward produces finite gradients that the Muon update accepts (smoke test of the combination)."""
+    from pithtrain_b200.modules.optimizer import Muon
+    from pithtrain_b200.ops.linear import Linear
+
+    torch.manual_seed(5)
+    lin = F8.FP8Linear(256, 256, bias=False, dtype=torch.bfloat16)
+    ref = Linear(256, 256, bias=False, dtype=torch.bfloat16)
+    ref.load_state_dict(lin.state_dict())
+    opt = Muon([lin.weight], lr=0.05, momentum=0.9, weight_decay=0.0)
+    before = lin.weight.detach().clone()
+    for _ in range(2):
+        y = lin(torch.randn(32, 256).bfloat16())
+        y.float().square().mean().backward()
+        assert torch.isfinite(lin.weight.grad.float()).all()
+        opt.step()
+        opt.zero_grad()
+        from pithtrain_b200.dualpipe.utils import FP8WeightCacheControl
+
+        FP8WeightCacheControl.step()  # weights changed: cached quantised copies are stale
+    assert torch.isfinite(lin.weight.float()).all() and not torch.equal(before, lin.weight.detach())
