@@ -58,6 +58,7 @@ SIGS = {
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
     "pt_rmsnorm_bwd": "PPPPPPPIIIP",
+    "pt_colsum_accumulate": "PIIIPIP",
     "pt_qk_norm_rope_fwd": "PPPPPPPPPPIIIIILFIP",
     "pt_qk_norm_rope_bwd_grid": "",
     "pt_qk_norm_rope_bwd": "PPPPPPPPPPPPIIIIILIP",

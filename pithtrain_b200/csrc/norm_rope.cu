@@ -355,3 +355,37 @@ PT_API int pt_qk_norm_rope_bwd(const void* dq, const void* dk, const void* qkv, 
         (const __nv_bfloat16*)sinb, pos, rstd_q, rstd_k, dw_partial, n_tokens, S, Hq, Hkv, qkv_stride, w_plus_one);
   return (int)cudaGetLastError();
 }
+
+// ----------------------------------------------------------------------------------------------
+// dst[c] += sum_g part[g, c]: finishes the per-block partial sums of a weight gradient (RMSNorm scale,
+// QK-norm scales) and accumulates into the gradient buffer in one launch.
+// ----------------------------------------------------------------------------------------------
+namespace pt {
+template <typename T>
+__global__ void __launch_bounds__(128)
+colsum_accumulate_kernel(const float* __restrict__ part, int G, int ld, int H, T* __restrict__ dst) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  int g = 0;
+  for (; g + 3 < G; g += 4) {
+    acc0 += part[(size_t)g * ld + c];
+    acc1 += part[(size_t)(g + 1) * ld + c];
+    acc2 += part[(size_t)(g + 2) * ld + c];
+    acc3 += part[(size_t)(g + 3) * ld + c];
+  }
+  for (; g < G; ++g) acc0 += part[(size_t)g * ld + c];
+  const float s = (acc0 + acc1) + (acc2 + acc3);
+  dst[c] = (T)((float)dst[c] + s);
+}
+}  // namespace pt
+
+// part: G rows of pitch ld floats; columns [0, H) of it are summed into dst[0:H).
+PT_API int pt_colsum_accumulate(const float* part, int G, int ld, int H, void* dst, int dst_fp32, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (G <= 0 || H <= 0) return 0;
+  int grid = (H + 127) / 128;
+  if (dst_fp32) pt::colsum_accumulate_kernel<float><<<grid, 128, 0, st>>>(part, G, ld, H, (float*)dst);
+  else pt::colsum_accumulate_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(part, G, ld, H, (__nv_bfloat16*)dst);
+  return (int)cudaGetLastError();
+}

@@ -45,3 +45,20 @@ def grad_buffer(p: torch.Tensor) -> torch.Tensor:
 
 def sp() -> int:
     return _native.stream_ptr()
+
+
+def accumulate_colsum(p: torch.Tensor, part: torch.Tensor, lo: int = 0, hi: int | None = None) -> None:
+    """``grad(p) += part[:, lo:hi].sum(0)`` for fp32 per-block partial sums ``part [G, C]``.
+
+    On CUDA with a flat gradient buffer this is one kernel that sums the partials and accumulates in
+    place; otherwise the reduction and :func:`accumulate_grad`.
+    """
+    hi = part.shape[1] if hi is None else hi
+    mg = getattr(p, "main_grad", None)
+    if (mg is not None and mg.is_cuda and part.is_cuda and mg.is_contiguous() and part.stride(1) == 1
+            and part.dtype == torch.float32 and mg.dtype in (torch.float32, torch.bfloat16) and mg.numel() == hi - lo):
+        rc = _native.lib().pt_colsum_accumulate(part.data_ptr() + 4 * lo, part.shape[0], part.stride(0), hi - lo,
+                                                mg.data_ptr(), int(mg.dtype == torch.float32), _native.stream_ptr())
+        _native.check(rc, "pt_colsum_accumulate")
+        return
+    accumulate_grad(p, part[:, lo:hi].sum(0))

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from .. import _native
-from .common import accumulate_grad, sp, use_native
+from .common import accumulate_colsum, accumulate_grad, sp, use_native
 
 
 def rmsnorm_ref(x, w, eps, residual=None, zero_centered=False):
@@ -75,7 +75,9 @@ class _RMSNormFn(torch.autograd.Function):
             rc = L.pt_rmsnorm_bwd(dy2.data_ptr(), None if dh2 is None else dh2.data_ptr(), h.data_ptr(), w.data_ptr(),
                                   rstd.data_ptr(), dx.data_ptr(), part.data_ptr(), n, H, int(ctx.zero_centered), sp())
             _native.check(rc, "pt_rmsnorm_bwd")
-            dw = part.sum(0)
+            dw = None
+            if ctx.needs_input_grad[1]:
+                accumulate_colsum(ctx.w_ref, part)
         else:
             hf, g = h.float(), dy2.float()
             xh = hf * rstd[:, None]
@@ -86,7 +88,7 @@ class _RMSNormFn(torch.autograd.Function):
             if dh2 is not None:
                 dx = dx + dh2.float()
             dx = dx.to(h.dtype)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and dw is not None:
             accumulate_grad(ctx.w_ref, dw)
         dx = dx.view(ctx.shape)
         return dx, None, None, (dx if ctx.has_res else None), None

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from .. import _native
-from .common import accumulate_grad, sp, use_native
+from .common import accumulate_colsum, accumulate_grad, sp, use_native
 
 
 def rotate_half(x):
@@ -95,9 +95,8 @@ class _QKNormRopeFn(torch.autograd.Function):
         else:
             dqkv[:, (Hq + Hkv) * D:].zero_()
         if has_norm:
-            dw = part.sum(0)
-            accumulate_grad(ctx.qw_ref, dw[:D])
-            accumulate_grad(ctx.kw_ref, dw[D:])
+            accumulate_colsum(ctx.qw_ref, part, 0, D)
+            accumulate_colsum(ctx.kw_ref, part, D, 2 * D)
         return (dqkv,) + (None,) * 11
 
 

@@ -265,3 +265,20 @@ def test_bounded_wait_reports_through_status_word():
     _native.check_status()  # cleared by the read
     y = bf(64, 64) + 1  # the context still works
     assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_accumulate_colsum_into_main_grad(dtype):
+    from pithtrain_b200.ops.common import accumulate_colsum
+
+    torch.manual_seed(12)
+    part = torch.randn(300, 256, device="cuda")
+    p = torch.nn.Parameter(torch.zeros(128, device="cuda", dtype=torch.bfloat16))
+    p.main_grad = torch.randn(128, device="cuda").to(dtype)
+    want = (p.main_grad.float() + part[:, 128:256].sum(0)).to(dtype)
+    accumulate_colsum(p, part, 128, 256)
+    _native.check_status()
+    assert torch.allclose(p.main_grad.float(), want.float(), atol=1e-2 if dtype == torch.bfloat16 else 1e-4, rtol=1e-2)
+    q = torch.nn.Parameter(torch.zeros(256, device="cuda", dtype=torch.bfloat16))  # no flat buffer: plain .grad
+    accumulate_colsum(q, part)
+    assert torch.allclose(q.grad.float(), part.sum(0), atol=0.2, rtol=2e-2)
