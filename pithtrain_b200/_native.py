@@ -69,7 +69,7 @@ SIGS = {
     "pt_gather_rows": "PPIPPIILP",
     "pt_combine": "PPPPPPIIIP",
     "pt_swiglu_fwd": "PPPIIIFFP",
-    "pt_swiglu_bwd": "PPPPPPPIIIFFP",
+    "pt_swiglu_bwd": "PPPPPPPIIIFFPP",
     "pt_cross_entropy": "PPPIILIP",
     "pt_scale_bf16": "PPLP",
     "pt_sumsq_grid": "",

@@ -381,12 +381,14 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __r
                   const float* __restrict__ row_w, __nv_bfloat16* __restrict__ dgu,
                   __nv_bfloat16* __restrict__ act_scaled, float* __restrict__ d_row_w,
                   const int* __restrict__ n_rows_ptr, int n_rows_max, int I, int interleaved,
-                  float alpha, float limit) {
+                  float alpha, float limit, const int* __restrict__ slot_of_row) {
   const int n_rows = n_rows_ptr ? min(*n_rows_ptr, n_rows_max) : n_rows_max;
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * wpb) {
-    const float wt = row_w ? row_w[r] : 1.f;
+    // with slot_of_row, row_w and d_row_w are indexed by the row's (token, slot) index instead of the row
+    const int widx = slot_of_row ? slot_of_row[r] : r;
+    const float wt = row_w ? (widx >= 0 ? row_w[widx] : 0.f) : 1.f;
     const __nv_bfloat16* row = gu + (size_t)r * 2 * I;
     __nv_bfloat16* drow = dgu + (size_t)r * 2 * I;
     float dot = 0.f;
@@ -426,7 +428,7 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __r
     }
     if (d_row_w) {
       dot = warp_sum(dot);
-      if (lane == 0) d_row_w[r] = dot;
+      if (lane == 0 && widx >= 0) d_row_w[widx] = dot;
     }
   }
 }
@@ -698,12 +700,12 @@ PT_API int pt_swiglu_fwd(const void* gu, void* act, const int* n_rows_ptr, int n
 
 PT_API int pt_swiglu_bwd(const void* gu, const void* dact, const float* row_w, void* dgu,
                          void* act_scaled, float* d_row_w, const int* n_rows_ptr, int n_rows_max,
-                         int I, int interleaved, float alpha, float limit, void* stream_) {
+                         int I, int interleaved, float alpha, float limit, const int* slot_of_row, void* stream_) {
   cudaStream_t st = (cudaStream_t)stream_;
   if (n_rows_max <= 0) return 0;
   if (I % 8 != 0) return -1;
   swiglu_bwd_kernel<<<grid_for(n_rows_max, 8, 16), 256, 0, st>>>((const __nv_bfloat16*)gu,
       (const __nv_bfloat16*)dact, row_w, (__nv_bfloat16*)dgu, (__nv_bfloat16*)act_scaled, d_row_w,
-      n_rows_ptr, n_rows_max, I, interleaved, alpha, limit);
+      n_rows_ptr, n_rows_max, I, interleaved, alpha, limit, slot_of_row);
   return (int)cudaGetLastError();
 }

@@ -168,19 +168,35 @@ def swiglu_fwd(gu: torch.Tensor, n_rows: Optional[torch.Tensor] = None, interlea
 
 def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor, row_w: Optional[torch.Tensor] = None,
                n_rows: Optional[torch.Tensor] = None, interleaved: bool = False, alpha: float = 1.0,
-               limit: float = 0.0, want_act: bool = False, want_dw: bool = False):
-    """Returns ``(dgu, act_scaled or None, d_row_w or None)``; see the kernel comment for semantics."""
+               limit: float = 0.0, want_act: bool = False, want_dw: bool = False,
+               slot_of_row: Optional[torch.Tensor] = None):
+    """Returns ``(dgu, act_scaled or None, d_row_w or None)``; see the kernel comment for semantics.
+
+    With ``slot_of_row`` the weights are given per (token, slot) (``row_w`` flat ``[n*k]``) and looked up
+    through the row's slot index (a pad row, index -1, has weight 0); ``d_row_w`` is then ``[n*k]`` too.
+    """
     R, I = gu.shape[0], gu.shape[1] // 2
+    if slot_of_row is not None and not (use_native(gu) and I % 8 == 0):
+        w_ext = torch.cat([row_w.reshape(-1).float(), row_w.new_zeros(1, dtype=torch.float32)])
+        dgu, act, d_rows = swiglu_bwd(gu, dact, w_ext[slot_of_row.long()], n_rows, interleaved, alpha, limit, want_act, want_dw)
+        dw = None
+        if d_rows is not None:
+            dw = torch.zeros(row_w.numel() + 1, dtype=torch.float32, device=gu.device)
+            dw[slot_of_row.long()] = d_rows  # index -1 (pad rows) lands in the spare last entry
+            dw = dw[:-1]
+        return dgu, act, dw
     if use_native(gu) and I % 8 == 0:
         dgu = torch.empty_like(gu)
         act = torch.empty((R, I), dtype=gu.dtype, device=gu.device) if want_act else None
-        dw = torch.zeros(R, dtype=torch.float32, device=gu.device) if want_dw else None
-        rw = None if row_w is None else row_w.float().contiguous()
+        n_w = R if slot_of_row is None else row_w.numel()
+        dw = torch.zeros(n_w, dtype=torch.float32, device=gu.device) if want_dw else None
+        rw = None if row_w is None else row_w.reshape(-1).float().contiguous()
         rc = _native.lib().pt_swiglu_bwd(gu.data_ptr(), dact.contiguous().data_ptr(), None if rw is None else rw.data_ptr(),
                                          dgu.data_ptr(), None if act is None else act.data_ptr(),
                                          None if dw is None else dw.data_ptr(),
                                          None if n_rows is None else n_rows.data_ptr(), R, I, int(interleaved),
-                                         float(alpha), float(limit), sp())
+                                         float(alpha), float(limit),
+                                         None if slot_of_row is None else slot_of_row.data_ptr(), sp())
         _native.check(rc, "pt_swiglu_bwd")
         return dgu, act, dw
     with torch.enable_grad():
@@ -295,10 +311,17 @@ class _MoEExpertsFn(torch.autograd.Function):
             del dq, dsc
         else:
             da = G.grouped_gemm_nn(dyg, ew.w2, offs)
-        w_ext = torch.cat([w.reshape(-1).float(), w.new_zeros(1, dtype=torch.float32)])
-        row_w = w_ext[slot_of_row.long()]  # -1 (pad) picks the appended zero
-        dgu, act_s, d_row_w = swiglu_bwd(gu, da, row_w, n_rows, ew.interleaved, ew.alpha, ew.limit,
-                                         want_act=True, want_dw=True)
+        plain = ew.b1 is None and ew.b2 is None
+        if plain:
+            # routing weights and their gradients are looked up / scattered through the slot index in the kernel
+            dgu, act_s, d_w_flat = swiglu_bwd(gu, da, w.reshape(-1), n_rows, ew.interleaved, ew.alpha, ew.limit,
+                                              want_act=True, want_dw=True, slot_of_row=slot_of_row)
+            d_row_w = row_w = None
+        else:
+            w_ext = torch.cat([w.reshape(-1).float(), w.new_zeros(1, dtype=torch.float32)])
+            row_w = w_ext[slot_of_row.long()]  # -1 (pad) picks the appended zero
+            dgu, act_s, d_row_w = swiglu_bwd(gu, da, row_w, n_rows, ew.interleaved, ew.alpha, ew.limit,
+                                             want_act=True, want_dw=True)
         del da
         if ew.b2 is not None:
             # y = act @ W2.T + b2 ; the routing-weight gradient also sees the bias term
@@ -307,8 +330,11 @@ class _MoEExpertsFn(torch.autograd.Function):
             accumulate_grad(ew.b2, segment_sum(dyg.float() * row_w[:, None], offs, E))
         if ew.b1 is not None:
             accumulate_grad(ew.b1, segment_sum(dgu, offs, E))
-        dw_ext = torch.cat([d_row_w, d_row_w.new_zeros(1)])
-        d_w = dw_ext[row_of_slot.long()].view(w.shape).to(w.dtype)
+        if plain:
+            d_w = d_w_flat.view(w.shape).to(w.dtype)
+        else:
+            dw_ext = torch.cat([d_row_w, d_row_w.new_zeros(1)])
+            d_w = dw_ext[row_of_slot.long()].view(w.shape).to(w.dtype)
         if ctx.fp8:
             _, _, q1t, s1t = F8.quantized_weight(ew.w1)
             gq, gsc = quant_rows(dgu, n_rows=n_rows)
