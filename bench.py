@@ -94,7 +94,7 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """The reference cannot run here: say why in one line (details in DESIGN.md)."""
+    """The reference cannot run here: say why in one line."""
     why = ("reference build unavailable on this box: pithtrain 0.1.3 needs deep-gemm (git), flash-attn-4[cu13], "
            "torch>=2.12 / CUDA 13; none is in the offline wheelhouse (pip install --no-index fails at dependency "
            "resolution, --no-deps installs a package that raises ModuleNotFoundError: deep_gemm on import)")

@@ -6,7 +6,7 @@ larger than the 126 MB L2 where the kernel is bandwidth-sensitive).
 
 Cases: gemm_dense (8192x8192x4096 bf16), gemm_grouped (128 experts x 256 rows, 1536x2048), wgrad_grouped
 (K-grouped with TMA reduce-add), gemm_fp8 (8192x8192x4096 e4m3), gemm_fp8_grouped, quant_rows, rmsnorm, swiglu,
-cross_entropy. Each case prints its CUDA-event time so the capture can be matched to an unprofiled number.
+cross_entropy, gather_rows, combine, route_sort, router_topk, qk_norm_rope. Each case prints its CUDA-event time so the capture can be matched to an unprofiled number.
 """
 
 import sys
@@ -83,6 +83,47 @@ def case_cross_entropy():
     logits = rand_bf16(4096, 151936)
     labels = torch.randint(0, 151936, (4096,), device="cuda")
     return (lambda: cross_entropy(logits, labels)), 0, 4096 * 151936 * 2 * 3
+
+
+def case_gather_rows():
+    from pithtrain_b200.ops.moe import gather_rows
+
+    x = rand_bf16(8192, 2048)
+    idx = torch.randint(0, 8192 * 8, (65536,), device="cuda", dtype=torch.int32)
+    return (lambda: gather_rows(x, idx, div=8)), 0, 65536 * 2048 * 2 * 2
+
+
+def case_combine():
+    from pithtrain_b200.ops.moe import combine_rows
+
+    y = rand_bf16(65536, 2048)
+    ros = torch.randperm(65536, device="cuda").int()
+    w = torch.rand(8192, 8, device="cuda")
+    return (lambda: combine_rows(y, ros, 8, w=w)), 0, (65536 + 8192) * 2048 * 2
+
+
+def case_route_sort():
+    from pithtrain_b200.ops.moe import route_sort
+
+    eids = torch.randint(0, 128, (65536, 8), device="cuda", dtype=torch.int32)
+    return (lambda: route_sort(eids, 128)), 0, 65536 * 8 * 4 * 4
+
+
+def case_router_topk():
+    from pithtrain_b200.ops.router import router_topk
+
+    logits = rand_bf16(65536, 128)
+    return (lambda: router_topk(logits, 8, "softmax_topk", True)), 0, 65536 * 128 * 2 + 65536 * (128 * 4 + 8 * 8)
+
+
+def case_qk_norm_rope():
+    from pithtrain_b200.ops.rope import qk_norm_rope
+
+    n, Hq, Hkv, D = 32768, 32, 4, 128
+    qkv = rand_bf16(n, (Hq + 2 * Hkv) * D)
+    qw, kw = torch.ones(D, device="cuda", dtype=torch.bfloat16), torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    cos, sin = rand_bf16(4096, D), rand_bf16(4096, D)
+    return (lambda: qk_norm_rope(qkv, qw, kw, cos, sin, Hq, Hkv, D, 1e-6, S=4096)), 0, n * (Hq + 2 * Hkv) * D * 2 * 2
 
 
 def main():
