@@ -125,8 +125,17 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 
 // ----------------------------------------------------------------------------------------------
 // Fused per-head RMSNorm (optional) + rotate-half RoPE for q and k, reading the fused qkv GEMM output.
-// One warp per (token, head). D in {64, 128}: PAIRS = D/64 rotation pairs per lane.
+// A head of D elements is handled by D/16 lanes: lane `sub` owns elements [8 sub, 8 sub + 8) of the first
+// half and their rotation partners in the second half, so every access is a 16-byte vector and the pair
+// (i, i + D/2) never leaves the lane. A warp covers 32 / (D/16) heads. D in {64, 128}: PAIRS = D / 64.
 // ----------------------------------------------------------------------------------------------
+template <int LPH>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPH / 2; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <int PAIRS>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
@@ -135,59 +144,62 @@ qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __
                         const __nv_bfloat16* __restrict__ sinb, const int* __restrict__ pos,
                         float* __restrict__ rstd_q, float* __restrict__ rstd_k, int n_tokens, int S,
                         int Hq, int Hkv, long long qkv_stride, float eps, int w_plus_one, int rot_dim) {
-  constexpr int D = PAIRS * 64;
-  const int half = D / 2;
-  const int lane = threadIdx.x & 31;
-  const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  constexpr int D = PAIRS * 64, HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;
+  const int lane = threadIdx.x & 31, sub = lane % LPH, i0 = sub * 8;
   const int heads = Hq + Hkv;
-  if (warp_id >= (long long)n_tokens * heads) return;
-  const int tok = (int)(warp_id / heads), hd = (int)(warp_id % heads);
+  const long long total = (long long)n_tokens * heads;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / LPH;
+  const bool live = item < total;
+  const long long it = live ? item : total - 1;
+  const int tok = (int)(it / heads), hd = (int)(it % heads);
   const bool is_q = hd < Hq;
   const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + (size_t)hd * D;  // k heads follow q heads
   __nv_bfloat16* dst = is_q ? q_out + ((size_t)tok * Hq + hd) * D : k_out + ((size_t)tok * Hkv + (hd - Hq)) * D;
   const __nv_bfloat16* wn = is_q ? qw : kw;
   const int p = pos ? pos[tok] : (tok % S);
-  float a[PAIRS], b[PAIRS];  // element i and its partner i + half
+  float a[8], b[8];
+  load8(src + i0, a);
+  load8(src + HALF + i0, b);
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < PAIRS; ++j) {
-    int i = lane + 32 * j;
-    a[j] = __bfloat162float(src[i]);
-    b[j] = __bfloat162float(src[i + half]);
-    ss += a[j] * a[j] + b[j] * b[j];
-  }
+  for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
   float rstd = 1.f;
   if (wn) {
-    ss = warp_sum(ss);
+    ss = group_sum<LPH>(ss);
     rstd = rsqrtf(ss / D + eps);
-    if (lane == 0) {
+    if (live && sub == 0) {
       if (is_q) rstd_q[(size_t)tok * Hq + hd] = rstd;
       else rstd_k[(size_t)tok * Hkv + (hd - Hq)] = rstd;
     }
   }
-  const int rhalf = rot_dim / 2;
+  float wa[8], wb[8], c[8], sn[8];
+  if (wn) {
+    load8(wn + i0, wa);
+    load8(wn + HALF + i0, wb);
+  }
+  const bool rotate = rot_dim == D;
+  if (rotate) {
+    load8(cosb + (size_t)p * D + i0, c);
+    load8(sinb + (size_t)p * D + i0, sn);
+  }
+  float oa[8], ob[8];
 #pragma unroll
-  for (int j = 0; j < PAIRS; ++j) {
-    int i = lane + 32 * j;
-    float na = a[j] * rstd, nb = b[j] * rstd;
+  for (int e = 0; e < 8; ++e) {
+    float na = a[e] * rstd, nb = b[e] * rstd;
     if (wn) {
-      float wa = __bfloat162float(wn[i]), wb = __bfloat162float(wn[i + half]);
-      if (w_plus_one) { wa += 1.f; wb += 1.f; }
-      na *= wa; nb *= wb;
+      float x = wa[e], y = wb[e];
+      if (w_plus_one) { x += 1.f; y += 1.f; }
+      na *= x; nb *= y;
     }
     // round like the unfused path (norm output is bf16 before the rotation)
     na = __bfloat162float(__float2bfloat16(na));
     nb = __bfloat162float(__float2bfloat16(nb));
-    float oa = na, ob = nb;
-    if (rot_dim == D) {
-      float c = __bfloat162float(cosb[(size_t)p * D + i]), s = __bfloat162float(sinb[(size_t)p * D + i]);
-      oa = na * c - nb * s;
-      ob = nb * c + na * s;
-    } else {
-      (void)rhalf;
-    }
-    dst[i] = __float2bfloat16(oa);
-    dst[i + half] = __float2bfloat16(ob);
+    oa[e] = rotate ? na * c[e] - nb * sn[e] : na;
+    ob[e] = rotate ? nb * c[e] + na * sn[e] : nb;
+  }
+  if (live) {
+    store8(dst + i0, oa);
+    store8(dst + HALF + i0, ob);
   }
 }
 
@@ -200,75 +212,81 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat1
                         const int* __restrict__ pos, const float* __restrict__ rstd_q,
                         const float* __restrict__ rstd_k, float* __restrict__ dw_partial,
                         int n_tokens, int S, int Hq, int Hkv, long long qkv_stride, int w_plus_one) {
-  constexpr int D = PAIRS * 64;
-  const int half = D / 2;
+  constexpr int D = PAIRS * 64, HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;
+  __shared__ float acc[2 * D];  // weight-gradient sums of this CTA: q scales then k scales
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int sub = lane % LPH, i0 = sub * 8;
   const int heads = Hq + Hkv;
   const long long total = (long long)n_tokens * heads;
-  float dwq_a[PAIRS], dwq_b[PAIRS], dwk_a[PAIRS], dwk_b[PAIRS];
+  for (int cidx = threadIdx.x; cidx < 2 * D; cidx += blockDim.x) acc[cidx] = 0.f;
+  __syncthreads();
+  float dwq_a[8], dwq_b[8], dwk_a[8], dwk_b[8];
 #pragma unroll
-  for (int j = 0; j < PAIRS; ++j) dwq_a[j] = dwq_b[j] = dwk_a[j] = dwk_b[j] = 0.f;
-  for (long long warp_id = (long long)blockIdx.x * wpb + wib; warp_id < total;
-       warp_id += (long long)gridDim.x * wpb) {
-    const int tok = (int)(warp_id / heads), hd = (int)(warp_id % heads);
+  for (int e = 0; e < 8; ++e) dwq_a[e] = dwq_b[e] = dwk_a[e] = dwk_b[e] = 0.f;
+  for (long long base = ((long long)blockIdx.x * wpb + wib) * HPW; base < total; base += (long long)gridDim.x * wpb * HPW) {
+    const long long item = base + lane / LPH;
+    const bool live = item < total;
+    const long long it = live ? item : total - 1;
+    const int tok = (int)(it / heads), hd = (int)(it % heads);
     const bool is_q = hd < Hq;
     const __nv_bfloat16* g = is_q ? dq + ((size_t)tok * Hq + hd) * D : dk + ((size_t)tok * Hkv + (hd - Hq)) * D;
     const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + (size_t)hd * D;
     __nv_bfloat16* dst = dqkv + (size_t)tok * qkv_stride + (size_t)hd * D;
     const __nv_bfloat16* wn = is_q ? qw : kw;
     const int p = pos ? pos[tok] : (tok % S);
-    float dna[PAIRS], dnb[PAIRS], xa[PAIRS], xb[PAIRS];
+    float ga[8], gb[8], c[8], sn[8], dna[8], dnb[8], xa[8], xb[8];
+    load8(g + i0, ga);
+    load8(g + HALF + i0, gb);
+    load8(cosb + (size_t)p * D + i0, c);
+    load8(sinb + (size_t)p * D + i0, sn);
     float rstd = 1.f;
     if (wn) rstd = is_q ? rstd_q[(size_t)tok * Hq + hd] : rstd_k[(size_t)tok * Hkv + (hd - Hq)];
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < PAIRS; ++j) {
-      int i = lane + 32 * j;
-      float ga = __bfloat162float(g[i]), gb = __bfloat162float(g[i + half]);
-      float c = __bfloat162float(cosb[(size_t)p * D + i]), s = __bfloat162float(sinb[(size_t)p * D + i]);
-      dna[j] = ga * c + gb * s;
-      dnb[j] = gb * c - ga * s;
-      if (wn) {
-        xa[j] = __bfloat162float(src[i]) * rstd;
-        xb[j] = __bfloat162float(src[i + half]) * rstd;
-        float wa = __bfloat162float(wn[i]), wb = __bfloat162float(wn[i + half]);
-        if (w_plus_one) { wa += 1.f; wb += 1.f; }
-        if (is_q) { dwq_a[j] += dna[j] * xa[j]; dwq_b[j] += dnb[j] * xb[j]; }
-        else { dwk_a[j] += dna[j] * xa[j]; dwk_b[j] += dnb[j] * xb[j]; }
-        dna[j] *= wa; dnb[j] *= wb;
-        dot += dna[j] * xa[j] + dnb[j] * xb[j];
-      }
+    for (int e = 0; e < 8; ++e) {
+      dna[e] = ga[e] * c[e] + gb[e] * sn[e];
+      dnb[e] = gb[e] * c[e] - ga[e] * sn[e];
     }
     if (wn) {
-      dot = warp_sum(dot) / D;
+      float wa[8], wb[8];
+      load8(src + i0, xa);
+      load8(src + HALF + i0, xb);
+      load8(wn + i0, wa);
+      load8(wn + HALF + i0, wb);
 #pragma unroll
-      for (int j = 0; j < PAIRS; ++j) {
-        dna[j] = rstd * (dna[j] - xa[j] * dot);
-        dnb[j] = rstd * (dnb[j] - xb[j] * dot);
+      for (int e = 0; e < 8; ++e) {
+        xa[e] *= rstd; xb[e] *= rstd;
+        float x = wa[e], y = wb[e];
+        if (w_plus_one) { x += 1.f; y += 1.f; }
+        if (live) {
+          if (is_q) { dwq_a[e] += dna[e] * xa[e]; dwq_b[e] += dnb[e] * xb[e]; }
+          else { dwk_a[e] += dna[e] * xa[e]; dwk_b[e] += dnb[e] * xb[e]; }
+        }
+        dna[e] *= x; dnb[e] *= y;
+        dot += dna[e] * xa[e] + dnb[e] * xb[e];
+      }
+      dot = group_sum<LPH>(dot) / D;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        dna[e] = rstd * (dna[e] - xa[e] * dot);
+        dnb[e] = rstd * (dnb[e] - xb[e] * dot);
       }
     }
-#pragma unroll
-    for (int j = 0; j < PAIRS; ++j) {
-      int i = lane + 32 * j;
-      dst[i] = __float2bfloat16(dna[j]);
-      dst[i + half] = __float2bfloat16(dnb[j]);
+    if (live) {
+      store8(dst + i0, dna);
+      store8(dst + HALF + i0, dnb);
     }
   }
   if (qw && dw_partial) {
-    // reduce the per-warp weight-gradient partials across the block, one row of 2*D per CTA
-    __shared__ float sm[8][2 * 128 + 2 * 128];
 #pragma unroll
-    for (int j = 0; j < PAIRS; ++j) {
-      int i = lane + 32 * j;
-      sm[wib][i] = dwq_a[j]; sm[wib][i + half] = dwq_b[j];
-      sm[wib][D + i] = dwk_a[j]; sm[wib][D + i + half] = dwk_b[j];
+    for (int e = 0; e < 8; ++e) {
+      atomicAdd(&acc[i0 + e], dwq_a[e]);
+      atomicAdd(&acc[HALF + i0 + e], dwq_b[e]);
+      atomicAdd(&acc[D + i0 + e], dwk_a[e]);
+      atomicAdd(&acc[D + HALF + i0 + e], dwk_b[e]);
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
-      float s = 0.f;
-      for (int wv = 0; wv < wpb; ++wv) s += sm[wv][c];
-      dw_partial[(size_t)blockIdx.x * 2 * D + c] = s;
-    }
+    for (int cidx = threadIdx.x; cidx < 2 * D; cidx += blockDim.x) dw_partial[(size_t)blockIdx.x * 2 * D + cidx] = acc[cidx];
   }
 }
 
@@ -321,7 +339,8 @@ PT_API int pt_qk_norm_rope_fwd(const void* qkv, void* q_out, void* k_out, const 
   cudaStream_t st = (cudaStream_t)stream_;
   if (n_tokens <= 0) return 0;
   if (D != 64 && D != 128) return -1;
-  long long warps = (long long)n_tokens * (Hq + Hkv);
+  const int heads_per_warp = 32 / (D / 16);
+  long long warps = ((long long)n_tokens * (Hq + Hkv) + heads_per_warp - 1) / heads_per_warp;
   int grid = (int)((warps + 7) / 8);
   if (D == 128)
     qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out,
