@@ -123,20 +123,6 @@ __global__ void ep_wait_acks_kernel(EpChan c, int slot, unsigned epoch, int* err
   if (s < c.ep && epoch > 2) wait_ge_bounded(chan_ack(c, c.rank, slot, s), epoch - 2, err);
 }
 
-// One warp copies a row of `vec` 16-byte vectors. Eight loads are issued before the first store so that a
-// row of 4 KB (hidden 2048, bf16) is one batch of independent loads per lane instead of eight dependent round trips.
-__device__ __forceinline__ void copy_row(uint4* __restrict__ d, const uint4* __restrict__ s, int vec, int lane) {
-  int v = lane;
-  for (; v + 7 * 32 < vec; v += 8 * 32) {
-    uint4 t[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) t[u] = s[v + 32 * u];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) d[v + 32 * u] = t[u];
-  }
-  for (; v < vec; v += 32) d[v] = s[v];
-}
-
 // Dispatch direction: gather rows by token index and store them into each destination's partition.
 __global__ void __launch_bounds__(256)
 ep_push_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __restrict__ src, long long src_stride,
@@ -151,7 +137,7 @@ ep_push_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __restri
       const int t = send_token_idx[(size_t)d * c.cap + r];
       const uint4* s4 = reinterpret_cast<const uint4*>(src + (size_t)t * src_stride);
       uint4* d4 = reinterpret_cast<uint4*>(chan_row(c, d, slot, c.rank, r));
-      copy_row(d4, s4, vec, lane);
+      for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
       if (c.k > 0 && lane < c.k) {
         chan_mi(c, d, slot, c.rank, r)[lane] = send_eids[((size_t)d * c.cap + r) * c.k + lane];
         chan_mf(c, d, slot, c.rank, r)[lane] = weights[(size_t)t * c.k + lane];
@@ -213,7 +199,7 @@ ep_compact_kernel(EpChan c, int slot, const int* __restrict__ prefix, unsigned c
       const int r = i - prefix[s];
       const uint4* s4 = reinterpret_cast<const uint4*>(chan_row(c, c.rank, slot, s, r));
       uint4* d4 = reinterpret_cast<uint4*>(out_rows + (size_t)i * c.W);
-      copy_row(d4, s4, vec, lane);
+      for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
       if (c.k > 0 && lane < c.k) {
         out_eids[(size_t)i * c.k + lane] = chan_mi(c, c.rank, slot, s, r)[lane];
         out_w[(size_t)i * c.k + lane] = chan_mf(c, c.rank, slot, s, r)[lane];
@@ -249,7 +235,7 @@ ep_return_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __rest
     const int r = i - prefix[s];
     const uint4* s4 = reinterpret_cast<const uint4*>(rows + (size_t)i * c.W);
     uint4* d4 = reinterpret_cast<uint4*>(chan_row(c, s, slot, c.rank, r));
-    copy_row(d4, s4, vec, lane);
+    for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
     if (c.k > 0 && meta_f && lane < c.k) chan_mf(c, s, slot, c.rank, r)[lane] = meta_f[(size_t)i * c.k + lane];
   }
   __threadfence_system();

@@ -297,46 +297,23 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < n; t += gridDim.x * wpb) {
-    // lane j keeps the row index and weight of slot j (k <= 32); they are broadcast when needed, so the
-    // index loads leave the inner loop and four row loads are in flight before the first accumulate
-    int my_r = -1;
-    float my_w = 0.f;
-    if (lane < k) {
-      my_r = row_of_slot[(size_t)t * k + lane];
-      my_w = w ? w[(size_t)t * k + lane] : 1.f;
-    }
-    for (int cb = 0; cb < H; cb += 256) {  // every lane runs the same trip count (shuffles inside)
-      const int c0 = cb + lane * 8;
-      const bool in = c0 < H;
+    for (int c0 = lane * 8; c0 < H; c0 += 256) {
       float acc[8];
-      if (res && in) load8(res + (size_t)t * H + c0, acc);
+      if (res) load8(res + (size_t)t * H + c0, acc);
       else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.f;
       }
-      for (int j = 0; j < k; j += 4) {
-        int r[4];
-        float wt[4], v[4][8];
+      for (int j = 0; j < k; ++j) {
+        int r = row_of_slot[(size_t)t * k + j];
+        if (r < 0) continue;
+        float wt = w ? w[(size_t)t * k + j] : 1.f;
+        float v[8];
+        load8(y + (size_t)r * H + c0, v);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int jj = min(j + u, 31);
-          r[u] = __shfl_sync(0xffffffffu, my_r, jj);
-          wt[u] = __shfl_sync(0xffffffffu, my_w, jj);
-          if (j + u >= k) r[u] = -1;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (r[u] >= 0 && in) load8(y + (size_t)r[u] * H + c0, v[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (r[u] >= 0 && in) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] += wt[u] * v[u][e];
-          }
-        }
+        for (int e = 0; e < 8; ++e) acc[e] += wt * v[e];
       }
-      if (in) store8(out + (size_t)t * H + c0, acc);
+      store8(out + (size_t)t * H + c0, acc);
     }
   }
 }
