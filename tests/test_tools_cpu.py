@@ -44,3 +44,25 @@ def test_profile_analyze(tmp_path, capsys):
     assert analyze.main([str(tmp_path), "--json", str(tmp_path / "o.json")]) == 0
     assert "communication overlapped" in capsys.readouterr().out and (tmp_path / "o.json").exists()
     assert analyze.intersect([(0, 10), (20, 30)], [(5, 25)]) == 10
+
+
+def test_benchmark_recipes(tmp_path):
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    from benchmarks.pretraining.recipes import MODELS, make_cfg, parse_mesh
+
+    m = parse_mesh("h100-8n8g/pp4-dp2-cp1-ep8-seq4096-bf16-hsdp")
+    assert (m["pp"], m["dp"], m["cp"], m["ep"], m["seq"], m["gpus"], m["hsdp"], m["gbs"]) == (4, 2, 1, 8, 4096, 64, True, 1024)
+    assert parse_mesh("b200-1n1g/pp1-dp1-cp1-ep1-seq4096-bf16-gbs32")["gbs"] == 32
+    for model, recipe in MODELS.items():
+        for mesh in recipe.meshes:
+            cfg = make_cfg(model, mesh, tmp_path)
+            d, t = cfg.distributed, cfg.training
+            pm = parse_mesh(mesh)
+            assert (d.pipeline_parallel_size, d.expert_parallel_size, d.context_parallel_size) == (pm["pp"], pm["ep"], pm["cp"])
+            assert t.benchmark and t.max_steps == 25 and t.sequence_length == pm["seq"] and t.dataset is None
+            assert t.global_batch_size % (pm["dp"] * pm["ep"]) == 0
+            assert t.global_batch_size // (pm["dp"] * pm["ep"]) >= 2 * pm["pp"]  # enough micro-batches for the V schedule
+    assert "yarn" in open(tmp_path / "benchmarks" / "gpt-oss-120b" / "model.json").read()
