@@ -282,3 +282,30 @@ def test_accumulate_colsum_into_main_grad(dtype):
     q = torch.nn.Parameter(torch.zeros(256, device="cuda", dtype=torch.bfloat16))  # no flat buffer: plain .grad
     accumulate_colsum(q, part)
     assert torch.allclose(q.grad.float(), part.sum(0), atol=0.2, rtol=2e-2)
+
+
+def test_attention_sinks_and_packed_paths_on_gpu():
+    """Sinks through the library flash kernel (rescaled log-sum-exp) and packed sequences document by document."""
+    from pithtrain_b200.ops import attention as A
+
+    torch.manual_seed(13)
+    B, S, Hq, Hkv, D = 2, 512, 8, 2, 64
+    q, k, v = [bf(B, S, h, D).requires_grad_() for h in (Hq, Hkv, Hkv)]
+    sinks = torch.randn(Hq, device="cuda", requires_grad=True)
+    go = bf(B, S, Hq, D)
+    out = A.attention(q, k, v, True, None, None, sinks, None)
+    got = (out,) + torch.autograd.grad(out, [q, k, v, sinks], go)
+    ref = A.attention_ref(q, k, v, True, None, None, sinks, None)
+    want = (ref,) + torch.autograd.grad(ref, [q, k, v, sinks], go)
+    from pithtrain_b200.ops import ring_attention as R
+
+    assert not R._LIB_BLOCKS_BROKEN, R._LIB_BLOCKS_ERROR
+    for a, b in zip(got, want):
+        assert calc_diff(a.float(), b.float()) < 3e-4
+    cu = torch.tensor([0, 100, 300, S], dtype=torch.int32, device="cuda")
+    out = A.attention(q, k, v, True, None, None, None, cu)
+    ref = A.attention_ref(q, k, v, True, None, None, None, cu)
+    assert calc_diff(out.float(), ref.float()) < 3e-4
+    out = A.attention(q, k, v, True, None, 127, sinks, None)  # GPT-OSS sliding-window layer: blocked form
+    ref = A.attention_ref(q, k, v, True, None, 127, sinks, None)
+    assert calc_diff(out.float(), ref.float()) < 3e-4

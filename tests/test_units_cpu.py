@@ -296,3 +296,34 @@ def test_reference_package_name_alias():
     import pithtrain_b200.contexts.distributed as ctx_impl
 
     assert ctx_alias is ctx_impl  # one module object: no duplicated global state
+
+
+@pytest.mark.parametrize("window,use_sinks,packed", [(127, True, False), (128, False, True), (5, True, True), (200, False, False)])
+def test_blocked_sliding_window_attention(window, use_sinks, packed):
+    from pithtrain_b200.ops.attention import attention, attention_ref, attention_window_blocked, segments_from_cu_seqlens
+
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, D = 2, 512, 4, 2, 16
+    q, k, v = [torch.randn(B, S, h, D, requires_grad=True) for h in (Hq, Hkv, Hkv)]
+    sinks = torch.randn(Hq, requires_grad=True) if use_sinks else None
+    cu = torch.tensor([0, 100, 300, S], dtype=torch.int32) if packed else None
+    ref = attention_ref(q, k, v, True, None, window, sinks, cu)
+    seg = segments_from_cu_seqlens(cu, S) if packed else None
+    out = attention_window_blocked(q, k, v, window, None, sinks, seg)
+    leaves = [q, k, v] + ([sinks] if use_sinks else [])
+    go = torch.randn_like(ref)
+    for a, b in zip((ref,) + torch.autograd.grad(ref, leaves, go), (out,) + torch.autograd.grad(out, leaves, go)):
+        assert torch.allclose(a, b, atol=2e-5, rtol=1e-4)
+    if S > 2 * (window + 128):  # the public entry point picks the blocked form by itself
+        assert torch.allclose(attention(q, k, v, True, None, window, sinks, cu), ref, atol=2e-5, rtol=1e-4)
+
+
+def test_attention_per_document_equals_masked_attention():
+    from pithtrain_b200.ops.attention import attention_per_document, attention_ref
+
+    torch.manual_seed(1)
+    q, k, v = torch.randn(1, 96, 4, 8), torch.randn(1, 96, 2, 8), torch.randn(1, 96, 2, 8)
+    cu = torch.tensor([0, 17, 64, 96], dtype=torch.int32)
+    sinks = torch.randn(4)
+    got = attention_per_document(q, k, v, cu, None, sinks, inner=attention_ref)
+    assert torch.allclose(got, attention_ref(q, k, v, True, None, None, sinks, cu), atol=1e-5)
