@@ -123,6 +123,7 @@ def main() -> int:
     ap.add_argument("--optimizer", default="muon")
     ap.add_argument("--resident-state-gb", type=float, default=22.0,
                     help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
+    ap.add_argument("--fp8", action="store_true", help="not the headline run: forward/dgrad GEMMs in block-scaled e4m3 (dtype says so)")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
     args = ap.parse_args()
     if args.impl == "reference":
@@ -159,6 +160,7 @@ def main() -> int:
     t.scheduler = make_constant_scheduler
     t.dataset = None  # synthetic uniform token ids
     t.grad_dtype = "bf16"
+    t.fp8 = bool(args.fp8)
     t.muon_momentum_dtype = "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
@@ -239,7 +241,7 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+            "vs_baseline": None, "dtype": ("fp8 e4m3 block-scaled forward/dgrad GEMMs, bf16 elsewhere" if args.fp8 else "bf16"), "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
             "tokens_per_sec_per_gpu": value / n, "mfu_of_measured_sustained_bf16": mfu,
             "config": {
                 "model": "Qwen3-30B-A3B architecture (48 layers, hidden 2048, 32q/4kv heads x128, 128 experts top-8, "

@@ -12,8 +12,20 @@ def calc_diff(x, y):
     return 0.0 if d == 0 else float(1 - 2 * (x * y).sum() / d)
 
 
-def test_qwen3_staged_vs_reference():
+@pytest.mark.parametrize("fp8", [False, True])
+def test_qwen3_staged_vs_reference(fp8):
+    """``fp8``: forward and input-gradient GEMMs of the projections and experts run block-scaled e4m3 (looser bound)."""
     from pithtrain_b200 import _native
+    from pithtrain_b200.ops import fp8_linear
+
+    fp8_linear.enable(fp8)
+    try:
+        _staged_vs_reference(_native, fp8)
+    finally:
+        fp8_linear.enable(False)
+
+
+def _staged_vs_reference(_native, fp8):
     from pithtrain_b200.contexts import distributed
     from pithtrain_b200.dualpipe.execution import ChunkRecord, model_backward, model_forward
     from pithtrain_b200.models.qwen3_moe import Qwen3MoeModel
@@ -46,13 +58,14 @@ def test_qwen3_staged_vs_reference():
         for v in vars(mod).values():
             if type(v).__name__ == "FusedWeights":
                 v.fused_grad = None
+    fp8_linear.enable(False)  # the oracle is bf16/fp32 math
     logits2 = m.reference_forward(ids)
     loss2 = torch.nn.functional.cross_entropy(logits2.view(-1, 2048).float(), labels.view(-1), reduction="sum")
     loss2.backward()
-    assert abs(float(loss) - float(loss2)) / float(loss2) < 5e-3
+    assert abs(float(loss) - float(loss2)) / float(loss2) < (2e-2 if fp8 else 5e-3)
     bad = []
     for n, p in m.named_parameters():
         d = calc_diff(g1[n], p.grad.float())
-        if d > 2e-2:
+        if d > (8e-2 if fp8 else 2e-2):
             bad.append((n, d))
     assert not bad, bad
