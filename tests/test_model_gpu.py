@@ -26,6 +26,8 @@ def test_qwen3_staged_vs_reference(fp8):
 
 
 def _staged_vs_reference(_native, fp8):
+    from pithtrain_b200.ops import fp8_linear
+
     from pithtrain_b200.contexts import distributed
     from pithtrain_b200.dualpipe.execution import ChunkRecord, model_backward, model_forward
     from pithtrain_b200.models.qwen3_moe import Qwen3MoeModel
