@@ -1,44 +1,81 @@
-"""Pipeline point-to-point helpers (NCCL/gloo isend-irecv batches).
+"""Pipeline point-to-point traffic: one pending batch of isend/irecv operations per executor.
 
-Activations and their gradients travelling between pipeline stages all have one static shape
-``(micro_batch, seq/cp, hidden)``, published once through :func:`set_p2p_tensor_shapes`
-(same contract as pithtrain/dualpipe/comm.py:14-49).
+Everything that crosses a pipeline boundary — an activation going down, a gradient coming back — has the same
+static signature ``(micro_batch, seq/cp, hidden)`` in the compute dtype. The signature is published once per job
+(:func:`set_p2p_tensor_shapes`, :func:`set_p2p_tensor_dtype`; the setter names are those of the reference,
+pithtrain/dualpipe/comm.py:14-25, because user code calls them). :class:`P2PBatch` collects the operations an
+executor posts between two compute actions and commits them as one ``batch_isend_irecv``.
 """
 
 from __future__ import annotations
 
-from typing import List, Tuple
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
 
-TENSOR_SHAPES: List[Tuple[int, ...]] = []
-TENSOR_DTYPE: torch.dtype = torch.bfloat16
+
+@dataclass
+class _Signature:
+    shapes: List[Tuple[int, ...]] = field(default_factory=list)
+    dtype: torch.dtype = torch.bfloat16
 
 
-def set_p2p_tensor_shapes(shapes: List[Tuple[int, ...]]) -> None:
-    global TENSOR_SHAPES
-    TENSOR_SHAPES = list(shapes)
+SIGNATURE = _Signature()
+
+
+def set_p2p_tensor_shapes(shapes: Sequence[Tuple[int, ...]]) -> None:
+    SIGNATURE.shapes = [tuple(s) for s in shapes]
 
 
 def set_p2p_tensor_dtype(dtype: torch.dtype) -> None:
-    global TENSOR_DTYPE
-    TENSOR_DTYPE = dtype
+    SIGNATURE.dtype = dtype
 
 
-def build_from_tensor_shapes(device) -> List[torch.Tensor]:
-    return [torch.empty(s, dtype=TENSOR_DTYPE, device=device, requires_grad=True) for s in TENSOR_SHAPES]
+def _global_rank(group, rank_in_group: int) -> int:
+    return rank_in_group if group is None else dist.get_global_rank(group, rank_in_group)
 
 
+class P2PBatch:
+    """Operations waiting for the next commit. ``recv`` hands out the landing buffers immediately; they are valid
+    after :meth:`commit`."""
+
+    def __init__(self, group, device) -> None:
+        self.group, self.device = group, device
+        self.ops: List[dist.P2POp] = []
+
+    def __bool__(self) -> bool:
+        return bool(self.ops)
+
+    def recv(self, src: int) -> List[torch.Tensor]:
+        peer = _global_rank(self.group, src)
+        landing = [torch.empty(shape, dtype=SIGNATURE.dtype, device=self.device, requires_grad=True) for shape in SIGNATURE.shapes]
+        self.ops.extend(dist.P2POp(dist.irecv, t, peer, self.group) for t in landing)
+        return landing
+
+    def send(self, tensors: Sequence[torch.Tensor], dst: int) -> None:
+        peer = _global_rank(self.group, dst)
+        self.ops.extend(dist.P2POp(dist.isend, t.detach().contiguous(), peer, self.group) for t in tensors)
+
+    def commit(self) -> None:
+        """Issue everything posted so far as one batch and wait for it."""
+        if not self.ops:
+            return
+        for req in dist.batch_isend_irecv(self.ops):
+            req.wait()
+        self.ops = []
+
+
+# function-style spellings used by older call sites
 def append_irecv(ops: list, src: int, group, device) -> List[torch.Tensor]:
-    tensors = build_from_tensor_shapes(device)
-    src = dist.get_global_rank(group, src) if group is not None else src
-    for t in tensors:
-        ops.append(dist.P2POp(dist.irecv, t, src, group))
-    return tensors
+    batch = P2PBatch(group, device)
+    out = batch.recv(src)
+    ops.extend(batch.ops)
+    return out
 
 
-def append_isend(ops: list, tensors: List[torch.Tensor], dst: int, group) -> None:
-    dst = dist.get_global_rank(group, dst) if group is not None else dst
-    for t in tensors:
-        ops.append(dist.P2POp(dist.isend, t.detach().contiguous(), dst, group))
+def append_isend(ops: list, tensors: Sequence[torch.Tensor], dst: int, group) -> None:
+    batch = P2PBatch(group, None)
+    batch.send(tensors, dst)
+    ops.extend(batch.ops)
