@@ -93,37 +93,68 @@ reduce_kernel(Chan c, unsigned epoch, float scale, double* sumsq_partials, int* 
     const int per = c.fp32 ? 4 : 8;  // elements per 16-byte vector
     const long long nvec = c.region / per;
     const long long base_bytes = (long long)c.rank * c.region * (c.fp32 ? 4 : 2);
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-      float acc[8];
+    // Four vectors per thread and iteration: all W x 4 loads are issued before the first add, so a thread
+    // keeps 4 W independent 16-byte loads in flight (peer loads take microseconds over NVLink).
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * stride) {
+      uint4 raw[U][MAXW > 8 ? 8 : MAXW];
+      float acc[U][8];
+      const int Wc = c.W;
+      for (int rb = 0; rb < Wc; rb += 8) {  // groups of up to 8 ranks keep the register footprint bounded
+        const int rn = min(8, Wc - rb);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int r = 0; r < c.W; ++r) {
-        const char* src = reinterpret_cast<const char*>(c.grad[r]) + base_bytes + v * 16;
-        uint4 u = (r == c.rank) ? *reinterpret_cast<const uint4*>(src) : ld_cg_v4(src);
-        if (c.fp32) {
-          acc[0] += __uint_as_float(u.x); acc[1] += __uint_as_float(u.y);
-          acc[2] += __uint_as_float(u.z); acc[3] += __uint_as_float(u.w);
-        } else {
-          float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), d = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
-          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-          acc[4] += d.x; acc[5] += d.y; acc[6] += e.x; acc[7] += e.y;
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + u * stride;
+          if (v < nvec) {
+            for (int r = 0; r < rn; ++r) {
+              const char* src = reinterpret_cast<const char*>(c.grad[rb + r]) + base_bytes + v * 16;
+              raw[u][r] = (rb + r == c.rank) ? *reinterpret_cast<const uint4*>(src) : ld_cg_v4(src);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (rb == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+          }
+          const long long v = v0 + u * stride;
+          if (v < nvec) {
+            for (int r = 0; r < rn; ++r) {
+              const uint4 x = raw[u][r];
+              if (c.fp32) {
+                acc[u][0] += __uint_as_float(x.x); acc[u][1] += __uint_as_float(x.y);
+                acc[u][2] += __uint_as_float(x.z); acc[u][3] += __uint_as_float(x.w);
+              } else {
+                float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), d = unpack_bf16x2(x.z), e = unpack_bf16x2(x.w);
+                acc[u][0] += a.x; acc[u][1] += a.y; acc[u][2] += b.x; acc[u][3] += b.y;
+                acc[u][4] += d.x; acc[u][5] += d.y; acc[u][6] += e.x; acc[u][7] += e.y;
+              }
+            }
+          }
         }
       }
-      char* dst = reinterpret_cast<char*>(c.grad[c.rank]) + base_bytes + v * 16;
-      uint4 o;
-      if (c.fp32) {
-        float f0 = acc[0] * scale, f1 = acc[1] * scale, f2 = acc[2] * scale, f3 = acc[3] * scale;
-        o = make_uint4(__float_as_uint(f0), __float_as_uint(f1), __float_as_uint(f2), __float_as_uint(f3));
-        local += (double)f0 * f0 + (double)f1 * f1 + (double)f2 * f2 + (double)f3 * f3;
-      } else {
-        o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
-        o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
-        // the norm is taken of the values as stored (rounded to bf16), like a separate pass would see
-        float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), d = unpack_bf16x2(o.z), e = unpack_bf16x2(o.w);
-        local += (double)a.x * a.x + (double)a.y * a.y + (double)b.x * b.x + (double)b.y * b.y +
-                 (double)d.x * d.x + (double)d.y * d.y + (double)e.x * e.x + (double)e.y * e.y;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * stride;
+        if (v >= nvec) continue;
+        char* dst = reinterpret_cast<char*>(c.grad[c.rank]) + base_bytes + v * 16;
+        uint4 o;
+        if (c.fp32) {
+          float f0 = acc[u][0] * scale, f1 = acc[u][1] * scale, f2 = acc[u][2] * scale, f3 = acc[u][3] * scale;
+          o = make_uint4(__float_as_uint(f0), __float_as_uint(f1), __float_as_uint(f2), __float_as_uint(f3));
+          local += (double)f0 * f0 + (double)f1 * f1 + (double)f2 * f2 + (double)f3 * f3;
+        } else {
+          o.x = pack_bf16x2(acc[u][0] * scale, acc[u][1] * scale); o.y = pack_bf16x2(acc[u][2] * scale, acc[u][3] * scale);
+          o.z = pack_bf16x2(acc[u][4] * scale, acc[u][5] * scale); o.w = pack_bf16x2(acc[u][6] * scale, acc[u][7] * scale);
+          // the norm is taken of the values as stored (rounded to bf16), like a separate pass would see
+          float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), d = unpack_bf16x2(o.z), e = unpack_bf16x2(o.w);
+          local += (double)a.x * a.x + (double)a.y * a.y + (double)b.x * b.x + (double)b.y * b.y +
+                   (double)d.x * d.x + (double)d.y * d.y + (double)e.x * e.x + (double)e.y * e.y;
+        }
+        *reinterpret_cast<uint4*>(dst) = o;
       }
-      *reinterpret_cast<uint4*>(dst) = o;
     }
   }
 #pragma unroll

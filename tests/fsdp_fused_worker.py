@@ -52,3 +52,41 @@ def run(rank: int, world: int, grad_dtype_name: str, rounds: int = 3):
         assert float(fused.flat_grad.abs().max()) == 0.0
     dist.barrier()
     fused.comm.close()
+    if rounds >= 3 and gdt == torch.bfloat16:
+        _report_bandwidth(rank, world, dev)
+
+
+def _report_bandwidth(rank: int, world: int, dev) -> None:
+    """Device-timed reduce-scatter and parameter publication of a 512 MB group (printed by rank 0)."""
+    from pithtrain_b200.parallel.flat_shard import FlatShardGroup
+
+    p = nn.Parameter(torch.zeros(world * 64 * 1024 * 1024 // world, device=dev, dtype=torch.bfloat16))
+    named = [(f"w{i}", nn.Parameter(torch.zeros(32 * 1024 * 1024, device=dev, dtype=torch.bfloat16))) for i in range(2 * world)]
+    g = FlatShardGroup("bw", named, [], dist.group.WORLD, world, rank, torch.bfloat16, device=dev, fused_collectives=True)
+    del p
+    region_bytes = g.region * 2
+    times = {"reduce": [], "push": []}
+    for it in range(6):
+        g.flat_grad.fill_(0.5)
+        dist.barrier()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        g.reduce_grads()
+        e[1].record()
+        g.gather_params()
+        g.wait_params()
+        e[2].record()
+        g.zero_grad()
+        torch.cuda.synchronize()
+        if it >= 2:
+            times["reduce"].append(e[0].elapsed_time(e[1]))
+            times["push"].append(e[1].elapsed_time(e[2]))
+    t = torch.tensor([min(times["reduce"]), min(times["push"])], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        remote = (world - 1) * region_bytes
+        print(f"[fsdp-fused bandwidth] W={world} region {region_bytes / 2**20:.0f} MiB: reduce-scatter {float(t[0]):.3f} ms "
+              f"({remote / float(t[0]) / 1e6:.0f} GB/s pulled per GPU), publish {float(t[1]):.3f} ms "
+              f"({remote / float(t[1]) / 1e6:.0f} GB/s pushed per GPU); measured peer copy 770 GB/s per direction", flush=True)
+    dist.barrier()
+    g.comm.close()
