@@ -66,3 +66,35 @@ def test_benchmark_recipes(tmp_path):
             assert t.global_batch_size % (pm["dp"] * pm["ep"]) == 0
             assert t.global_batch_size // (pm["dp"] * pm["ep"]) >= 2 * pm["pp"]  # enough micro-batches for the V schedule
     assert "yarn" in open(tmp_path / "benchmarks" / "gpt-oss-120b" / "model.json").read()
+
+
+def test_wandb_run_helpers_with_fake_api(tmp_path, capsys):
+    from pithtrain_b200.tools.wandb_tracking import runs as W
+
+    class FakeFile:
+        def __init__(self, name): self.name = name
+        def download(self, root, replace):
+            open(f"{root}/{self.name}", "w").write("log")
+
+    class FakeRun:
+        def __init__(self, rid, name, vals):
+            self.id, self.name, self.state, self.lastHistoryStep, self._v = rid, name, "finished", len(vals) - 1, vals
+        def scan_history(self, keys):
+            return [{"_step": i, keys[1]: v} for i, v in enumerate(self._v)]
+        def file(self, name): return FakeFile(name)
+
+    class FakeApi:
+        def runs(self, project):
+            return [FakeRun("aaa111", "base", [12.0, 11.5, 11.0]), FakeRun("bbb222", "feature", [12.0, 11.6, 10.9, 10.5])]
+
+    api = FakeApi()
+    assert W.main(["list", "me/proj"], api=api) == 0
+    assert "2 runs" in capsys.readouterr().out
+    assert W.main(["compare", "me/proj", "--metric", "train/cross-entropy-loss", "--ref", "base", "--runs", "bbb222"], api=api) == 0
+    out = capsys.readouterr().out
+    assert "3 common steps" in out and "max +0.1" in out and "min -0.1" in out
+    assert W.main(["files", "me/proj", "--runs", "feature", "--out", str(tmp_path)], api=api) == 0
+    assert (tmp_path / "feature" / "output.log").read_text() == "log"
+    import pytest as _pytest
+    with _pytest.raises(SystemExit):
+        W.resolve(api, "me/proj", "nope")
