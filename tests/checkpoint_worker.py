@@ -13,14 +13,22 @@ MODEL = dict(model_type="qwen3_moe", hidden_size=32, num_attention_heads=2, num_
              vocab_size=64, num_hidden_layers=4, max_position_embeddings=32, rope_theta=1e4, attention_bias=False)
 
 
-def make_cfg(pp, ep, save_location, steps):
+def model_config(key):
+    if key == "qwen3":
+        return dict(MODEL)
+    from dualpipev_worker import CONFIGS
+
+    return dict(CONFIGS[key])
+
+
+def make_cfg(pp, ep, save_location, steps, model="qwen3"):
     from pithtrain_b200.modules.training import make_muon_optimizer, make_wsd_scheduler
     from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg
 
     cfg = PretrainLMCfg()
     cfg.distributed.pipeline_parallel_size, cfg.distributed.expert_parallel_size = pp, ep
     t = cfg.training
-    t.model, t.sequence_length, t.lr, t.max_steps = dict(MODEL), 16, 1e-2, steps
+    t.model, t.sequence_length, t.lr, t.max_steps = model_config(model), 16, 1e-2, steps
     t.micro_batch_size, t.global_batch_size = 1, 4 * ep
     t.optimizer, t.scheduler = make_muon_optimizer, partial(make_wsd_scheduler, warmup_ratio=0.5)
     t.param_dtype, t.save_location = "fp32", Path(save_location)
@@ -34,7 +42,7 @@ def full_state(model):
     return {k: v.detach().clone() for k, v in to_canonical_model(dict(model.state_dict()), model).items()}
 
 
-def run(rank, world, pp, ep, save_location, phase):
+def run(rank, world, pp, ep, save_location, phase, model="qwen3"):
     from pithtrain_b200.contexts import training
     from pithtrain_b200.modules.checkpoint import load_training_checkpoint, save_training_checkpoint, to_canonical_optim
     from pithtrain_b200.modules.distributed import setup_distributed
@@ -42,7 +50,7 @@ def run(rank, world, pp, ep, save_location, phase):
     from pithtrain_b200.modules.training import setup_training
     from pithtrain_b200.tasks.pretrain_lm import train_step
 
-    cfg = make_cfg(pp, ep, save_location, 4)
+    cfg = make_cfg(pp, ep, save_location, 4, model)
     setup_logging(cfg)
     setup_distributed(cfg, failfast=False)
     setup_training(cfg)

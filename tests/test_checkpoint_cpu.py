@@ -22,3 +22,72 @@ def test_reshard_roundtrip(tmp_path, save_layout, load_layout):
     (pp0, ep0), (pp1, ep1) = save_layout, load_layout
     launch(pp0 * ep0, checkpoint_worker.run, pp0, ep0, str(tmp_path), "save")
     launch(pp1 * ep1, checkpoint_worker.run, pp1, ep1, str(tmp_path), "load")
+
+
+@pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
+def test_muon_state_roundtrip_other_families(tmp_path, model):
+    """Muon momentum and AdamW moments of the MLA / shared-expert / dense-first-layer model and of the model with
+    expert biases survive a save at pp2·ep2 and a load at pp1·ep2 (pithtrain tests/test_muon_checkpoint.py:109-125)."""
+    launch(4, checkpoint_worker.run, 2, 2, str(tmp_path), "save", model)
+    launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load", model)
+
+
+def test_param_group_membership_survives_canonical_roundtrip():
+    """Which optimizer a parameter belongs to, its hyper-parameters and its state survive canonical -> localized, with
+    stacked expert parameters fanned out to global expert indices (pithtrain tests/test_muon.py:164-206)."""
+    from pithtrain_b200.modules.checkpoint import to_canonical_optim, to_localized_optim
+    from pithtrain_b200.modules.optimizer import AdamW, Muon
+    from pithtrain_b200.modules.training import is_muon_param
+
+    class Experts(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = torch.nn.Module()
+            self.gate_proj.weight = torch.nn.Parameter(torch.randn(2, 6, 8))
+
+    def build():
+        torch.manual_seed(0)
+        layer = torch.nn.Module()
+        layer.self_attn = torch.nn.Module()
+        layer.self_attn.q_proj = torch.nn.Linear(8, 8, bias=True)
+        layer.input_layernorm = torch.nn.Module()
+        layer.input_layernorm.weight = torch.nn.Parameter(torch.ones(8))
+        layer.mlp = torch.nn.Module()
+        layer.mlp.experts = Experts()
+        layer.mlp.gate = torch.nn.Linear(8, 4, bias=False)
+        stage = torch.nn.Module()
+        stage.layers = torch.nn.ModuleDict({"1": layer})
+        model = torch.nn.Module()  # the pipeline wrapper names its stages ``module.<N>``
+        model.module = torch.nn.Sequential(stage)
+        named = list(model.named_parameters())
+        muon = [p for n, p in named if is_muon_param(n, p)]
+        rest = [p for n, p in named if not is_muon_param(n, p)]
+        return model, (Muon(muon, lr=0.02, momentum=0.9, weight_decay=0.1), AdamW(rest, lr=0.01, weight_decay=0.0))
+
+    model, opts = build()
+    for p in model.parameters():
+        p.grad = torch.randn_like(p)
+    for o in opts:
+        o.step()
+    canon = to_canonical_optim(opts, model, ep_rank=1)
+    groups = {g["type"]: g for g in canon["param_groups"]}
+    assert set(groups["Muon"]["params"]) == {"layers.1.self_attn.q_proj.weight", "layers.1.mlp.experts.2.gate_proj.weight",
+                                             "layers.1.mlp.experts.3.gate_proj.weight"}
+    assert set(groups["AdamW"]["params"]) == {"layers.1.self_attn.q_proj.bias", "layers.1.input_layernorm.weight",
+                                              "layers.1.mlp.gate.weight"}
+    assert groups["Muon"]["lr"] == 0.02 and groups["AdamW"]["lr"] == 0.01
+    stacked = opts[0].state[model.module[0].layers["1"].mlp.experts.gate_proj.weight]
+    field = next(k for k, v in stacked.items() if torch.is_tensor(v) and v.shape == (2, 6, 8))
+    assert torch.equal(canon["state"]["layers.1.mlp.experts.3.gate_proj.weight"][field], stacked[field][1])
+
+    model2, opts2 = build()
+    opts2[0].param_groups[0]["lr"] = 99.0
+    to_localized_optim(canon, model2, opts2, ep_rank=1)
+    assert opts2[0].param_groups[0]["lr"] == 0.02
+    again = to_canonical_optim(opts2, model2, ep_rank=1)
+    assert [g["params"] for g in again["param_groups"]] == [g["params"] for g in canon["param_groups"]]
+    assert again["state"].keys() == canon["state"].keys()
+    for k, entry in canon["state"].items():
+        for f, v in entry.items():
+            if torch.is_tensor(v):
+                assert torch.equal(again["state"][k][f].float(), v.float()), (k, f)
