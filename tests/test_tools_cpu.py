@@ -1,4 +1,5 @@
 """Developer tools: log comparison."""
+import pytest
 from pithtrain_b200.tools.validate_correctness import compare
 
 LINE = ("[2026-01-01 00:00:0{i}] step 0000000{i}/00000025 | step-time {t} sec | cross-entropy-loss {ce} | "
@@ -98,3 +99,67 @@ def test_wandb_run_helpers_with_fake_api(tmp_path, capsys):
     import pytest as _pytest
     with _pytest.raises(SystemExit):
         W.resolve(api, "me/proj", "nope")
+
+
+def test_wandb_saved_views_with_fake_graphql(capsys):
+    """list / create / edit / show / delete against an in-memory stand-in for the project's view store."""
+    import json
+
+    from pithtrain_b200.tools.wandb_tracking import views as V
+
+    class Run:
+        def __init__(self, id, name): self.id, self.name = id, name
+
+    class Api:
+        def runs(self, path): return [Run("r1", "base"), Run("r2", "feature"), Run("r3", "ablation")]
+
+    store = {}
+
+    def graphql(doc, variables):
+        if "allViews" in doc:
+            return {"project": {"allViews": {"edges": [{"node": dict(v)} for v in store.values()]}}}
+        if "upsertView" in doc:
+            inp = variables["input"]
+            inserted = "id" not in inp
+            vid = inp.get("id") or f"view{len(store)}"
+            store[vid] = {"id": vid, "name": inp["name"], "displayName": inp["displayName"], "spec": inp["spec"]}
+            assert inp["type"] == "project-view" and inp["entityName"] == "team" and inp["projectName"] == "proj"
+            return {"upsertView": {"view": store[vid], "inserted": inserted}}
+        if "deleteView" in doc:
+            return {"deleteView": {"success": store.pop(variables["input"]["id"], None) is not None}}
+        raise AssertionError(doc)
+
+    assert V.slug_of("nw-abc123-v") == "abc123" and V.slug_of("report-7") is None and V.name_of("q") == "nw-q-v"
+    assert V.main(["create", "team/proj", "--name", "base vs feature", "--runs", "base,r2"], api=Api(), graphql=graphql) == 0
+    (view,) = store.values()
+    slug = V.slug_of(view["name"])
+    spec = json.loads(view["spec"])
+    assert spec["section"]["runSets"][0]["selections"] == {"root": 1, "bounds": [], "tree": ["r3"]}
+    assert V.split_runs(spec, {"r1": "base", "r2": "feature", "r3": "ablation"}) == (["base", "feature"], ["ablation"])
+    # a second view copies the layout of the first and gets a link of its own
+    spec["section"]["panelBankConfig"]["sections"] = [{"name": "train"}]
+    view["spec"] = json.dumps(spec)
+    assert V.main(["create", "team/proj", "--name", "only ablation", "--runs", "ablation", "--like", slug], api=Api(), graphql=graphql) == 0
+    assert len(store) == 2
+    other = [v for v in store.values() if v["displayName"] == "only ablation"][0]
+    ospec = json.loads(other["spec"])
+    assert ospec["section"]["panelBankConfig"]["sections"] == [{"name": "train"}]
+    assert ospec["section"]["runSets"][0]["selections"]["tree"] == ["r1", "r2"]
+    assert ospec["section"]["runSets"][0]["id"] != spec["section"]["runSets"][0]["id"]
+    # editing keeps name (and therefore the link), changes the hide-list and optionally the title
+    assert V.main(["edit", "team/proj", slug, "--runs", "r3,r1", "--name", "renamed"], api=Api(), graphql=graphql) == 0
+    assert len(store) == 2 and view["id"] in store
+    edited = store[view["id"]]
+    assert edited["name"] == V.name_of(slug) and edited["displayName"] == "renamed"
+    assert json.loads(edited["spec"])["section"]["runSets"][0]["selections"]["tree"] == ["r2"]
+    capsys.readouterr()
+    assert V.main(["show", "team/proj", slug], api=Api(), graphql=graphql) == 0
+    out = capsys.readouterr().out
+    assert "visible: ablation, base" in out and "hidden : feature" in out
+    assert V.main(["list", "team/proj"], api=Api(), graphql=graphql) == 0
+    assert capsys.readouterr().out.count("?nw=") == 2
+    assert V.main(["delete", "team/proj", slug], api=Api(), graphql=graphql) == 0 and len(store) == 1
+    with pytest.raises(SystemExit):
+        V.main(["show", "team/proj", slug], api=Api(), graphql=graphql)
+    with pytest.raises(SystemExit):
+        V.main(["create", "team/proj", "--name", "x", "--runs", "nope"], api=Api(), graphql=graphql)
