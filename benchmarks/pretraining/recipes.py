@@ -38,14 +38,16 @@ MODELS: Dict[str, ModelRecipe] = {
     "qwen3-30b-a3b": ModelRecipe("qwen3-30b-a3b", "qwen3", "global-batch", meshes=[
         "b200-1n1g/pp1-dp1-cp1-ep1-seq4096-bf16-gbs32", "b200-1n2g/pp1-dp1-cp1-ep2-seq4096-bf16-gbs64",
         "b200-1n4g/pp1-dp1-cp1-ep4-seq4096-bf16-gbs128", "b200-1n8g/pp2-dp1-cp1-ep4-seq4096-bf16-gbs256",
+        "b200-1n8g/pp2-dp1-cp1-ep4-seq4096-fp8-gbs256",
         "b200-1n8g/pp1-dp1-cp1-ep8-seq4096-bf16", "h100-2n8g/pp2-dp1-cp1-ep8-seq2048-bf16",
         "h100-4n8g/pp4-dp1-cp1-ep8-seq4096-bf16", "h100-8n8g/pp4-dp2-cp1-ep8-seq4096-bf16-hsdp"]),
     "deepseek-v2-lite": ModelRecipe("deepseek-v2-lite", "deepseek-v2", "sequence", 3e-3, meshes=[
-        "b200-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16", "b200-1n8g/pp1-dp1-cp2-ep4-seq8192-bf16", "h100-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16"]),
+        "b200-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16", "b200-1n8g/pp1-dp1-cp1-ep8-seq4096-fp8", "b200-1n8g/pp1-dp1-cp2-ep4-seq8192-bf16",
+        "h100-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16"]),
     "gpt-oss-120b": ModelRecipe("gpt-oss-120b", "gpt-oss", "micro-batch", overrides=YARN_GPT_OSS, meshes=[
         "b200-4n8g/pp4-dp1-cp1-ep8-seq2048-bf16", "h100-8n8g/pp8-dp1-cp1-ep8-seq2048-bf16"]),
     "gpt-oss-20b": ModelRecipe("gpt-oss-20b", "gpt-oss", "micro-batch", overrides=YARN_GPT_OSS, meshes=[
-        "b200-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16"]),
+        "b200-1n8g/pp1-dp1-cp1-ep8-seq2048-bf16", "b200-1n8g/pp1-dp1-cp4-ep2-seq32768-fp8-gbs64"]),
     "qwen3.5-35b-a3b": ModelRecipe("qwen3.5-35b-a3b", "qwen3.5", "global-batch", meshes=[
         "b200-1n8g/pp1-dp1-cp1-ep8-seq3072-bf16", "h100-2n8g/pp2-dp1-cp1-ep8-seq1536-bf16", "h100-4n8g/pp4-dp1-cp1-ep8-seq3072-bf16"]),
 }

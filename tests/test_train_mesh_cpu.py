@@ -13,9 +13,9 @@ from utilities import launch
 import train_worker
 
 
-def _curve(tmp_path, name, world, pp, ep, cp, strategy="fsdp", optimizer="adamw"):
+def _curve(tmp_path, name, world, pp, ep, cp, strategy="fsdp", optimizer="adamw", model="qwen3"):
     out = tmp_path / f"{name}.json"
-    launch(world, train_worker.run, pp, ep, cp, strategy, str(out), optimizer, timeout=420.0)
+    launch(world, train_worker.run, pp, ep, cp, strategy, str(out), optimizer, 4, model, timeout=420.0)
     return json.load(open(out))
 
 
@@ -43,3 +43,14 @@ def test_muon_dp2_ep2_matches_single_process(tmp_path):
     b = _curve(tmp_path, "muon4", 4, 1, 2, 1, optimizer="muon")
     for x, y in zip(a, b):
         assert abs(x["loss"] - y["loss"]) < 1e-3 * abs(x["loss"]), (a, b)
+
+
+@pytest.mark.parametrize("model,world,ep,cp", [("gpt_oss", 4, 2, 2), ("deepseek", 2, 1, 2)])
+def test_other_families_under_context_parallel(tmp_path, model, world, ep, cp):
+    """GPT-OSS (sinks + sliding windows through the ring, which the reference refuses: pithtrain/models/gpt_oss.py:361-362)
+    at cp2·ep2 and DeepSeek-V2 (MLA latent ring) at cp2 reproduce their single-process loss curves."""
+    a = _curve(tmp_path, f"{model}1", 1, 1, 1, 1, model=model)
+    b = _curve(tmp_path, f"{model}{world}", world, 1, ep, cp, model=model)
+    for step, (x, y) in enumerate(zip(a, b)):
+        assert abs(x["loss"] - y["loss"]) < 3e-4 * abs(x["loss"]), (model, step, a, b)
+        assert abs(x["gradient_norm"] - y["gradient_norm"]) < 3e-3 * abs(x["gradient_norm"]), (model, step, a, b)

@@ -5,7 +5,7 @@ import json
 
 
 def run(rank: int, world: int, pp: int, ep: int, cp: int, strategy: str, out_path: str, optimizer: str = "adamw",
-        steps: int = 4):
+        steps: int = 4, model: str = "qwen3"):
     from pithtrain_b200.contexts import training
     from pithtrain_b200.modules.distributed import setup_distributed
     from pithtrain_b200.modules.logging import setup_logging
@@ -22,6 +22,10 @@ def run(rank: int, world: int, pp: int, ep: int, cp: int, strategy: str, out_pat
                    rms_norm_eps=1e-6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
                    norm_topk_prob=True, vocab_size=128, num_hidden_layers=4, max_position_embeddings=64,
                    rope_theta=1e6, attention_bias=False)
+    if model != "qwen3":
+        from dualpipev_worker import CONFIGS
+
+        t.model = dict(CONFIGS[model])
     t.sequence_length, t.micro_batch_size, t.global_batch_size = 32, 1, 8
     t.lr, t.max_steps = 2e-3, steps
     t.optimizer = make_muon_optimizer if optimizer == "muon" else make_adamw_optimizer
