@@ -54,3 +54,7 @@ def test_other_families_under_context_parallel(tmp_path, model, world, ep, cp):
     for step, (x, y) in enumerate(zip(a, b)):
         assert abs(x["loss"] - y["loss"]) < 3e-4 * abs(x["loss"]), (model, step, a, b)
         assert abs(x["gradient_norm"] - y["gradient_norm"]) < 3e-3 * abs(x["gradient_norm"]), (model, step, a, b)
+
+
+def test_tiny_cpu_configuration_one_step():
+    launch(1, train_worker.run_tiny_cpu_step, timeout=300.0)

@@ -43,3 +43,81 @@ def run(rank: int, world: int, pp: int, ep: int, cp: int, strategy: str, out_pat
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(rows, f)
+
+
+TINY_CPU = dict(model_type="qwen3_moe", num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=64, rms_norm_eps=1e-6, rope_theta=1e6, num_experts=8, num_experts_per_tok=2,
+                moe_intermediate_size=128, norm_topk_prob=True, vocab_size=1024, max_position_embeddings=128,
+                attention_bias=False)
+
+
+def run_tiny_cpu_step(rank: int, world: int):
+    """Tiny Qwen3-MoE decoder (2 layers, hidden 256, 4 query / 2 KV heads of dim 64, 8 experts top-2, FFN 128, vocab
+    1024), batch 2 x 128, fp32: one forward + cross-entropy backward + AdamW step (lr 3e-4) through the public task
+    API, checked against the whole model on one device with ``torch.optim.AdamW``."""
+    from functools import partial
+    from types import SimpleNamespace
+
+    import torch
+
+    from pithtrain_b200.contexts import distributed, training
+    from pithtrain_b200.models import MODEL_CLASSES
+    from pithtrain_b200.modules.checkpoint import strip_prefix
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import make_adamw_optimizer, make_constant_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg, get_global_batch, train_step
+
+    cfg = PretrainLMCfg()
+    t = cfg.training
+    t.model, t.dataset = dict(TINY_CPU), None
+    t.sequence_length, t.micro_batch_size, t.global_batch_size = 128, 1, 2
+    t.lr, t.max_steps, t.moe_load_balance_coef = 3e-4, 1, 0.0
+    t.optimizer, t.scheduler = partial(make_adamw_optimizer, weight_decay=0.01), make_constant_scheduler
+    t.param_dtype, t.grad_dtype = "fp32", "fp32"
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    before = {strip_prefix(k): v.detach().clone() for k, v in training.model.state_dict().items()}
+    tokens, labels = (x.clone() for x in get_global_batch(cfg, distributed.device))
+    assert tokens.shape == (2, 128) and int(tokens.max()) < 1024
+    metrics = train_step(cfg)
+    after = {strip_prefix(k): v.detach().clone() for k, v in training.model.state_dict().items()}
+
+    full = MODEL_CLASSES["qwen3_moe"](SimpleNamespace(**TINY_CPU), -1)
+    missing = full.load_state_dict({k: v for k, v in before.items() if k in full.state_dict()}, strict=False)
+    assert not [k for k in missing.missing_keys if "inv_freq" not in k and "cos" not in k and "sin" not in k], missing
+    opt = torch.optim.AdamW(full.parameters(), lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    loss = 0.0
+    for i in range(2):
+        logits = full.reference_forward(tokens[i:i + 1])
+        loss = loss + torch.nn.functional.cross_entropy(logits.view(-1, 1024).float(), labels[i].long(), reduction="sum")
+    loss = loss / labels.numel()
+    loss.backward()
+    norm = torch.nn.utils.clip_grad_norm_(full.parameters(), t.max_grad_norm)
+    opt.step()
+    assert abs(float(loss.detach()) - metrics["loss"]) < 1e-5 * float(loss), (float(loss), metrics["loss"])
+    assert abs(float(norm) - metrics["gradient_norm"]) < 1e-4 * float(norm), (float(norm), metrics["gradient_norm"])
+    want = full.state_dict()
+    moved = 0
+    for k, v in after.items():
+        if k not in want:
+            continue
+        # the first AdamW step moves an element by lr * g / (|g| + eps): where |g| is of the order of eps the fp32
+        # summation order shows, so the bulk is held to 1e-6 and single elements to a fraction of lr
+        err = (v - want[k]).abs()
+        assert float(err.mean()) < 1e-6 and float(err.max()) < 1e-4, (k, float(err.mean()), float(err.max()))
+        moved += int(not torch.equal(v, before[k]))
+    assert moved >= 20, moved
+    # first moments are 0.1 * gradient: an eps-free comparison of every gradient the step produced
+    names = {id(p): strip_prefix(n) for n, p in training.model.named_parameters()}
+    grads = {n: p.grad for n, p in full.named_parameters()}
+    checked = 0
+    for opt_mine in training.optimizers:
+        for p, st in opt_mine.state.items():
+            n = names[id(p)]
+            if n in grads and "exp_avg" in st:
+                # the oracle's gradient was clipped in place by clip_grad_norm_ above, like the framework's
+                assert torch.allclose(st["exp_avg"], 0.1 * grads[n], atol=1e-9, rtol=2e-3), n
+                checked += 1
+    assert checked >= 20, checked
