@@ -39,3 +39,30 @@ def bench(fn, iters: int = 20, warmup: int = 5) -> float:
 
 def rand_bf16(*shape):
     return (torch.randn(*shape, device="cuda") * 0.5).bfloat16()
+
+
+def make_routing(tokens: int, experts: int, k: int, kind: str = "uniform", seed: int = 0, zipf_a: float = 1.2) -> torch.Tensor:
+    """``[tokens, k]`` int32 expert ids on the CPU, ``k`` distinct experts per token.
+
+    ``uniform``: every subset equally likely. ``normal``: top-k of router logits drawn from N(0, 1) (near-uniform load).
+    ``zipf``: expert ``e`` is picked with probability proportional to ``1 / (e + 1) ** zipf_a`` without replacement
+    (Gumbel top-k), so the first ranks of an expert-parallel group receive most of the traffic.
+    """
+    g = torch.Generator().manual_seed(seed)
+    if kind == "uniform":
+        return torch.rand(tokens, experts, generator=g).topk(k, dim=-1).indices.int()
+    if kind == "normal":
+        return torch.randn(tokens, experts, generator=g).topk(k, dim=-1).indices.int()
+    if kind == "zipf":
+        logp = -zipf_a * torch.log(torch.arange(1, experts + 1, dtype=torch.float32))
+        u = torch.rand(tokens, experts, generator=g).clamp_(1e-12, 1 - 1e-7)
+        return (logp - torch.log(-torch.log(u))).topk(k, dim=-1).indices.int()
+    raise ValueError(f"unknown routing {kind!r}")
+
+
+def remote_rows_by_destination(idx: torch.Tensor, experts: int, ep: int, rank: int) -> torch.Tensor:
+    """``[ep]`` int64: de-duplicated rows that source rank ``rank`` stores into each other GPU for routing ``idx``."""
+    dest = idx.long() // (experts // ep)
+    hit = torch.zeros(idx.shape[0], ep, dtype=torch.bool).scatter_(1, dest, True)
+    hit[:, rank] = False
+    return hit.sum(0)

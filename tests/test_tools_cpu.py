@@ -163,3 +163,22 @@ def test_wandb_saved_views_with_fake_graphql(capsys):
         V.main(["show", "team/proj", slug], api=Api(), graphql=graphql)
     with pytest.raises(SystemExit):
         V.main(["create", "team/proj", "--name", "x", "--runs", "nope"], api=Api(), graphql=graphql)
+
+
+def test_benchmark_routing_generators():
+    import torch
+
+    from benchmarks.operators.utilities import make_routing, remote_rows_by_destination
+
+    loads = {}
+    for kind in ("uniform", "normal", "zipf"):
+        idx = make_routing(2048, 128, 8, kind, seed=3)
+        assert idx.shape == (2048, 8) and idx.dtype == torch.int32
+        assert bool((idx.sort(-1).values.diff(dim=-1) > 0).all())  # k distinct experts per token
+        assert torch.equal(idx, make_routing(2048, 128, 8, kind, seed=3))
+        loads[kind] = torch.bincount(idx.flatten().long(), minlength=128).float()
+    assert float(loads["uniform"].max() / loads["uniform"].mean()) < 1.5
+    assert float(loads["normal"].max() / loads["normal"].mean()) < 1.5
+    assert float(loads["zipf"].max() / loads["zipf"].mean()) > 8 and int(loads["zipf"].argmax()) == 0
+    rows = remote_rows_by_destination(make_routing(1000, 16, 2, "uniform", seed=0), 16, 4, 1)
+    assert int(rows[1]) == 0 and rows.shape == (4,) and int(rows.sum()) <= 2000
