@@ -275,8 +275,25 @@ def train_step(cfg: PretrainLMCfg) -> dict:
 
     if t.save_interval is not None and t.save_location is not None and training.step % t.save_interval == 0:
         save_checkpoint(cfg)
-    gc.collect()
+    _collect_garbage()
     return metrics
+
+
+_STEPS_RUN = 0
+
+
+def _collect_garbage() -> None:
+    """Per-step collection (the automatic collector is off while training, so that no pause lands inside a step).
+
+    A full collection walks every tracked object of the process — a few hundred thousand, almost all of them modules,
+    the model, optimizer state and caches that live until the end — and takes ≈ 0.1 s with the GPU idle behind the
+    step's synchronize. After the second step of a process everything alive is moved to the permanent generation
+    (``gc.freeze``): later collections only look at what a step created and take about a millisecond."""
+    global _STEPS_RUN
+    gc.collect()
+    _STEPS_RUN += 1
+    if _STEPS_RUN == 2:
+        gc.freeze()
 
 
 # ------------------------------------------------------------------------------------------------
