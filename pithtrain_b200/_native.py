@@ -105,6 +105,7 @@ SIGS = {
     "pt_quant_rows": "PLPIPIIPPLP",
     "pt_quant_blocks": "PIIIPPPPP",
     "pt_gemm_fp8": "PPPIIIILLLLPLPPIIIIP",
+    "pt_attn_fwd_causal": "PPPPPIIIILLLLFP",
 }
 
 _CT = {"P": c_void_p, "I": c_int, "L": c_longlong, "F": c_float}

@@ -1,4 +1,5 @@
 """Memory-bound sm_100a kernels vs fp32 PyTorch references."""
+import os
 import pytest
 import torch
 
@@ -309,3 +310,24 @@ def test_attention_sinks_and_packed_paths_on_gpu():
     out = A.attention(q, k, v, True, None, 127, sinks, None)  # GPT-OSS sliding-window layer: blocked form
     ref = A.attention_ref(q, k, v, True, None, 127, sinks, None)
     assert calc_diff(out.float(), ref.float()) < 3e-4
+
+
+@pytest.mark.skipif(os.environ.get("PITHTRAIN_OWN_ATTENTION", "0") != "1",
+                    reason="the tcgen05 attention forward runs only with PITHTRAIN_OWN_ATTENTION=1 until it is validated")
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 4, 2), (2, 1024, 8, 2), (1, 4096, 8, 1)])
+def test_own_causal_attention_forward(B, S, Hq, Hkv):
+    from pithtrain_b200.ops import attention_native as N
+    from pithtrain_b200.ops.attention import attention_ref
+
+    torch.manual_seed(11)
+    qkv = bf(B, S, (Hq + 2 * Hkv) * 128, scale=1.0)  # slices of one projection output, like the model's
+    q = qkv[..., :Hq * 128].view(B, S, Hq, 128).requires_grad_()
+    k = qkv[..., Hq * 128:(Hq + Hkv) * 128].view(B, S, Hkv, 128)
+    v = qkv[..., (Hq + Hkv) * 128:].view(B, S, Hkv, 128)
+    assert N.causal_d128_supported(q, k, v, True, None, None, None)
+    out, lse = N.causal_d128_attention(q, k, v, True, None, None, None, None, return_lse=True)
+    torch.cuda.synchronize()
+    _native.check_status()
+    ref, ref_lse = attention_ref(q, k, v, causal=True, return_lse=True)
+    assert calc_diff(out.float(), ref.float()) < 1e-3
+    assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)

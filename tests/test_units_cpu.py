@@ -327,3 +327,27 @@ def test_attention_per_document_equals_masked_attention():
     sinks = torch.randn(4)
     got = attention_per_document(q, k, v, cu, None, sinks, inner=attention_ref)
     assert torch.allclose(got, attention_ref(q, k, v, True, None, None, sinks, cu), atol=1e-5)
+
+
+def test_own_attention_is_opt_in_and_shape_gated():
+    """The tcgen05 attention forward is registered only by an explicit switch, and its predicate accepts exactly the
+    layouts the kernel's tensor maps can describe."""
+    import os
+
+    from pithtrain_b200.ops import attention_native as N
+
+    if os.environ.get("PITHTRAIN_OWN_ATTENTION", "0") != "1":
+        assert N._IMPL is None
+    qkv = torch.zeros(2, 256, (8 + 2 * 2) * 128, dtype=torch.bfloat16)
+    q = qkv[..., :1024].view(2, 256, 8, 128)
+    k = qkv[..., 1024:1280].view(2, 256, 2, 128)
+    v = qkv[..., 1280:].view(2, 256, 2, 128)
+    ok = N.causal_d128_supported
+    assert ok(q, k, v, True, None, None, None)
+    assert not ok(q, k, v, False, None, None, None) and not ok(q, k, v, True, 127, None, None)
+    assert not ok(q, k, v, True, None, torch.zeros(8), None) and not ok(q, k, v, True, None, None, torch.tensor([0, 256]))
+    assert not ok(q.float(), k, v, True, None, None, None)
+    assert not ok(q[:, :200], k[:, :200], v[:, :200], True, None, None, None)  # not a multiple of 128
+    assert not ok(q.transpose(1, 2).contiguous().transpose(1, 2), k, v, True, None, None, None)  # head-major storage
+    assert not ok(q[..., :64], k[..., :64], v[..., :64], True, None, None, None)
+    assert not N.supported(q, k, v, True, None, None, None)  # CPU tensors never take the kernel
