@@ -1,8 +1,10 @@
 """Import-compatibility alias for scripts written against the reference package name.
 
 ``import pithtrain.tasks.pretrain_lm`` resolves to ``pithtrain_b200.tasks.pretrain_lm``, and the reference's
-``pithtrain.operators`` sub-package to ``pithtrain_b200.ops`` (module names inside follow this framework:
-``ring_attention``, ``cross_entropy``, ``grouped_linear``, ``linear`` ...). The alias is a meta-path finder
+``pithtrain.operators`` sub-package to ``pithtrain_b200.ops``, which also carries the reference's operator module
+names (``silu_mul``, ``clamped_swiglu``, ``indexed_bias_add``, ``flash_attn_v4``, ``all_to_all``, ``token_scatter``,
+``deepgemm_quantize`` next to ``ring_attention``, ``cross_entropy``, ``grouped_linear``, ``linear``,
+``gated_delta_rule``). The alias is a meta-path finder
 that hands out the already-imported implementation modules, so both names refer to the same objects and
 module-level state (contexts, caches) is never duplicated.
 """
@@ -28,10 +30,15 @@ class _AliasLoader(importlib.abc.Loader):
         self.target = target
 
     def create_module(self, spec):
-        return importlib.import_module(self.target)
+        module = importlib.import_module(self.target)
+        self._own_spec = module.__spec__
+        return module
 
-    def exec_module(self, module):  # the implementation module is already initialised
-        pass
+    def exec_module(self, module):
+        # The implementation module is already initialised. The import system has just stamped the alias spec on
+        # it; put its own spec back so that relative imports executed later (inside functions) still see a
+        # ``__package__`` that matches ``__spec__.parent``.
+        module.__spec__ = self._own_spec
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):

@@ -77,3 +77,13 @@ class GroupedLinear(nn.Module):
 
     def extra_repr(self) -> str:
         return f"groups={self.num_groups}, in={self.in_features}, out={self.out_features}"
+
+
+def __getattr__(name: str):
+    # ``FP8GroupedLinear`` lives with the fp8 path; the reference exports it from this module
+    # (pithtrain/operators/grouped_linear.py:239), so it resolves here too, lazily to keep the imports acyclic.
+    if name == "FP8GroupedLinear":
+        from .fp8_linear import FP8GroupedLinear
+
+        return FP8GroupedLinear
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -251,3 +251,13 @@ class _CatBias(torch.autograd.Function):
             accumulate_grad(b, g[off:off + b.numel()])
             off += b.numel()
         return tuple(None for _ in ctx.biases)
+
+
+def __getattr__(name: str):
+    # ``FP8Linear`` lives with the fp8 path; the reference exports it from this module
+    # (pithtrain/operators/linear.py:170), so it resolves here too, lazily to keep the imports acyclic.
+    if name == "FP8Linear":
+        from .fp8_linear import FP8Linear
+
+        return FP8Linear
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -105,3 +105,32 @@ def test_fp8_gradients_feed_muon():
 
         FP8WeightCacheControl.step()  # weights changed: cached quantised copies are stale
     assert torch.isfinite(lin.weight.float()).all() and not torch.equal(before, lin.weight.detach())
+
+
+def test_reference_named_quantiser_wrappers():
+    """Output shapes and contents of the casts under the reference's names (pithtrain/operators/deepgemm_quantize.py)."""
+    from pithtrain_b200.ops import deepgemm_quantize as DQ
+
+    torch.manual_seed(7)
+    x = (torch.randn(256, 300) * 2).bfloat16()
+    tok, tok_s, ch, ch_s = DQ.fp8cast_rowwise_colwise(x)
+    assert tok.shape == (256, 300) and tok_s.shape == (256, 3) and ch.shape == (256, 300) and ch_s.shape == (2, 300)
+    q_ref, s_ref = Q.quant_rows_ref(x)
+    assert torch.equal(tok.float(), q_ref.float()) and torch.equal(tok_s, s_ref.t())
+    # column-wise: every 128x1 column segment has its own power-of-two scale
+    seg = x.float().view(2, 128, 300).abs().amax(1)
+    assert torch.equal(ch_s, Q.pow2_scale_ref(seg))
+    assert torch.equal(ch.float(), (x.float().view(2, 128, 300) / ch_s[:, None, :]).view(256, 300).to(torch.float8_e4m3fn).float())
+    _, _, t, t_s = DQ.fp8cast_rowwise_transpose(x)
+    assert t.shape == (300, 256) and t_s.shape == (300, 2) and torch.equal(t.float(), ch.t().float())
+    _, _, bt, bt_s = DQ.fp8cast_rowwise_blockwise_transpose(x)
+    assert bt.shape == (300, 256) and bt_s.shape == (3, 2)
+    q, s, qt, st = DQ.fp8cast_blockwise_transpose(x)
+    assert q.shape == (256, 300) and s.shape == (2, 3) and qt.shape == (300, 256) and st.shape == (3, 2)
+    assert torch.equal(qt.float(), bt.float()) and torch.equal(st, bt_s) and torch.equal(qt.float(), q.t().float())
+    q3, s3, q3t, s3t = DQ.fp8cast_blockwise_transpose_batched(torch.stack([x, -x]))
+    assert q3.shape == (2, 256, 300) and s3t.shape == (2, 3, 2) and torch.equal(q3[0].float(), -q3[1].float())
+    offs = torch.tensor([128, 256], dtype=torch.int32)
+    _, _, flat, km_s = DQ.fp8cast_rowwise_kmajor(x, offs)
+    assert flat.shape == (256 * 300,) and km_s.shape == (300, 2)
+    assert torch.equal(flat[:128 * 300].view(300, 128).float(), ch[:128].t().float())
