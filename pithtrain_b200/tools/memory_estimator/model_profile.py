@@ -35,6 +35,7 @@ class ParallelCfg:
     offload_optimizer_state: bool = False
     resident_state_gb: float = 0.0  # with offload: GiB of optimizer state kept on the device anyway
     ep_backend: str = "fused"  # "fused" (symmetric buffers) or "nccl"
+    fp8_training: bool = False  # block-scaled e4m3 forward / input-gradient GEMMs: cached quantised weight copies
     capacity_factor: float = 1.5
 
     @property
@@ -178,11 +179,12 @@ class StaticMemory:
     grads: int = 0
     optimizer_device: int = 0
     optimizer_host: int = 0
+    fp8_weights: int = 0
     detail: Dict[str, int] = field(default_factory=dict)
 
     @property
     def device_total(self) -> int:
-        return self.params + self.grads + self.optimizer_device
+        return self.params + self.grads + self.optimizer_device + self.fp8_weights
 
 
 def chunk_layers(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> Tuple[range, range]:
@@ -193,11 +195,13 @@ def chunk_layers(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> Tuple[range
 
 def static_memory(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> StaticMemory:
     c0, c1 = chunk_layers(dims, par, pp_rank)
-    dense = expert = 0
+    dense = expert = quantised = 0
     for idx in list(c0) + list(c1):
         ls = dims.layer_shape(idx)
         dense += ls.attn_params + ls.dense_mlp_params + ls.shared_params + ls.router_params + ls.norm_params
         expert += ls.expert_params_per_expert * (dims.E // par.ep)
+        # projections and expert matrices take the fp8 path; routers, norms, embedding and lm_head stay bf16
+        quantised += ls.attn_params + ls.dense_mlp_params + ls.shared_params + ls.expert_params_per_expert * (dims.E // par.ep)
     edge = 0
     if pp_rank == 0:
         edge += dims.V * dims.H  # embedding on the first stage
@@ -207,6 +211,10 @@ def static_memory(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> StaticMemo
     out = StaticMemory()
     out.params = 2 * (dense + expert)
     out.grads = gb * (dense + expert)
+    if par.fp8_training:
+        # one e4m3 byte per element in each orientation (forward reads W, the input gradient reads W^T), cached for the
+        # whole step; the fp32 scales add 1/4096 of that
+        out.fp8_weights = int(2 * quantised * (1 + 4 / (128 * 128)))
     dense_owned = dense / (par.dp * par.cp * par.ep)
     expert_owned = expert / (par.dp * par.cp)
     if par.optimizer == "adamw":

@@ -35,7 +35,8 @@ def summary_lines(est: Estimate, dims: ModelDims, par: ParallelCfg, pp_rank: int
            f"micro-batches in flight at most: chunk0 {est.max_inflight[0]}, chunk1 {est.max_inflight[1]}; "
            f"one micro-batch holds {fmt(est.chunk_bytes[0]).strip()} / {fmt(est.chunk_bytes[1]).strip()}", ""]
     for name, b in est.categories().items():
-        out.append(f"  {name:<52s}{fmt(b)}")
+        if b or not name.startswith("fp8"):
+            out.append(f"  {name:<52s}{fmt(b)}")
     out.append(f"  {'-' * 52}{'-' * 12}")
     out.append(f"  {'estimated peak (at ' + est.peak_event.action + ', action #' + str(est.peak_event.step) + ')':<52s}{fmt(est.peak_total)}")
     if est.static.optimizer_host:

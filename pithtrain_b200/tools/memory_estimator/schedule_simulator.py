@@ -48,6 +48,7 @@ class Estimate:
     def categories(self) -> Dict[str, int]:
         return {"parameters": self.static.params, "gradient accumulators": self.static.grads,
                 "optimizer state (device)": self.static.optimizer_device,
+                "fp8 weight copies (both orientations)": self.static.fp8_weights,
                 "activations + deferred wgrad at peak": self.peak_activations, "transient workspace": self.transient,
                 "communication buffers": self.comm_buffers, "runtime (context, NCCL, cuBLAS/cuDNN workspaces)": self.runtime_overhead}
 
