@@ -362,3 +362,6 @@ def setup_training(cfg: object) -> None:
     setup_model(t, cfg.distributed)
     training.optimizers = t.optimizer(t)
     training.schedulers = t.scheduler(t)
+    from ..tools.memory_trace import attach_from_env
+
+    attach_from_env(training.model)  # PITHTRAIN_MEMORY_TRACE=<ranks>: one line of memory figures per pipeline action

