@@ -60,6 +60,8 @@ def zeropower_via_newtonschulz5(Gm: torch.Tensor, steps: int = 5) -> torch.Tenso
       transposing copy.
     """
     assert Gm.ndim >= 2
+    if _own_gemm_usable(Gm):
+        return newtonschulz5_own_gemm(Gm, steps)
     a, b, c = 3.4445, -4.7750, 2.0315
     G = Gm.to(torch.bfloat16)
     squeeze = G.ndim == 2
@@ -94,6 +96,66 @@ def zeropower_via_newtonschulz5(Gm: torch.Tensor, steps: int = 5) -> torch.Tenso
                     out = X
     out = out.reshape(*lead, out.shape[-2], out.shape[-1])
     return out.squeeze(0) if squeeze else out
+
+
+def newtonschulz5_own_gemm(Gm: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """The same iteration on this package's own tcgen05 GEMM family instead of the library's batched products.
+
+    A stack ``[E, r, c]`` is one row-grouped problem: ``Y Y^T`` (wide) is an M-grouped NT product of the rows of every
+    matrix against itself, ``Y^T Y`` (tall) a K-grouped TN product, ``A A`` an M-grouped NT product (``A`` is
+    symmetric), and the update ``(B + aI) Y`` / ``Y (B + aI)`` an M-grouped NN product — the operand layouts of the
+    forward, input-gradient and weight-gradient GEMMs of a grouped linear layer. ``Y`` stays in the input's
+    orientation throughout, so neither case needs a transposed copy. Selected for CUDA inputs by
+    ``PITHTRAIN_NS_GEMM=own``; not the default until it has been timed against the batched library products.
+    """
+    from ..ops import gemm as G_
+
+    a, b, c = 3.4445, -4.7750, 2.0315
+    G = Gm.to(torch.bfloat16)
+    lead = G.shape[:-2]
+    G = G.reshape(-1, G.shape[-2], G.shape[-1]).contiguous()
+    E, r, cdim = G.shape
+    wide = r <= cdim
+    m = r if wide else cdim
+    dev = G.device
+    nrm = torch.linalg.vector_norm(G, dim=(-2, -1), keepdim=True, dtype=torch.float32)
+    s = 1.0 / (nrm + 1e-7)
+    s1, s2 = s.to(G.dtype), (s * s).to(G.dtype)
+    offs_r = (torch.arange(E + 1, device=dev, dtype=torch.int32) * r)
+    offs_m = (torch.arange(E + 1, device=dev, dtype=torch.int32) * m)
+    Y = G.view(E * r, cdim)
+    eye_a = None
+    for it in range(max(steps, 0)):
+        Y3 = Y.view(E, r, cdim)
+        if wide:
+            A = G_.grouped_gemm_nt(Y, Y3, offs_r).view(E, m, m)
+        else:
+            A = G_.grouped_gemm_tn(Y, Y, offs_r, torch.zeros((E, m, m), dtype=G.dtype, device=dev), accumulate=True)
+        if it == 0:
+            A = A * s2
+        A2 = A.reshape(E * m, m)
+        AA = G_.grouped_gemm_nt(A2, A.contiguous(), offs_m).view(E, m, m)
+        B = b * A + c * AA
+        B.diagonal(dim1=-2, dim2=-1).add_(a)
+        if it == 0:
+            B = B * s1
+        B = B.contiguous()
+        if wide:
+            Y = G_.grouped_gemm_nn(B.view(E * m, m), Y3, offs_m)  # (B + aI) Y
+        else:
+            Y = G_.grouped_gemm_nn(Y, B, offs_r)  # Y (B + aI)
+    if steps <= 0:
+        Y = (G * s1).view(E * r, cdim)
+    return Y.view(*lead, r, cdim)
+
+
+def _own_gemm_usable(G: torch.Tensor) -> bool:
+    import os
+
+    if os.environ.get("PITHTRAIN_NS_GEMM", "library") != "own" or not G.is_cuda:
+        return False
+    r, c = G.shape[-2], G.shape[-1]
+    return min(r, c) % 64 == 0 and r % 16 == 0 and c % 8 == 0
 
 
 def muon_scale_factor(n: int, m: int) -> float:

@@ -351,3 +351,24 @@ def test_own_attention_is_opt_in_and_shape_gated():
     assert not ok(q.transpose(1, 2).contiguous().transpose(1, 2), k, v, True, None, None, None)  # head-major storage
     assert not ok(q[..., :64], k[..., :64], v[..., :64], True, None, None, None)
     assert not N.supported(q, k, v, True, None, None, None)  # CPU tensors never take the kernel
+
+
+@pytest.mark.parametrize("shape", [(3, 64, 128), (2, 128, 64), (64, 64), (1, 192, 64)])
+def test_newton_schulz_on_grouped_gemm_products_matches_batched(shape):
+    """The formulation on M-/K-grouped GEMMs (wide and tall, stacks and single matrices) is the same iteration."""
+    from pithtrain_b200.modules.optimizer import newtonschulz5_own_gemm, zeropower_via_newtonschulz5
+
+    torch.manual_seed(3)
+    G = torch.randn(*shape)
+    got = newtonschulz5_own_gemm(G).float()
+    want = zeropower_via_newtonschulz5(G).float()
+    assert got.shape == want.shape
+    # two bf16 evaluations of the same polynomial (A^2 is rounded before it is combined here, after there)
+    assert float((got - want).abs().max()) < 0.06 and float((got - want).norm() / want.norm()) < 0.05
+    sv = torch.linalg.svdvals(got)
+    assert float(sv.max()) < 1.5
+    if shape[-1] != shape[-2]:  # a square Gaussian matrix has singular values near zero that five steps cannot lift
+        assert float(sv.min()) > 0.5
+    U, _, Vh = torch.linalg.svd(G.float(), full_matrices=False)
+    polar = U @ Vh
+    assert float((got * polar).sum() / (got.norm() * polar.norm())) > 0.97
