@@ -28,6 +28,12 @@ CONFIGS = {
                      first_k_dense_replace=1, intermediate_size=96, routed_scaling_factor=1.0, topk_method="greedy",
                      n_group=1, topk_group=1, vocab_size=96, num_hidden_layers=4, max_position_embeddings=64,
                      rope_theta=10000.0, rope_scaling=None),
+    "qwen35": dict(model_type="qwen3_5_moe_text", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                   attn_output_gate=True, layer_types=["linear_attention", "full_attention"] * 2, linear_conv_kernel_dim=4,
+                   linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4,
+                   num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+                   rope_parameters=dict(rope_type="default", rope_theta=1e6, partial_rotary_factor=0.5), rms_norm_eps=1e-6,
+                   attention_bias=False, vocab_size=96, num_hidden_layers=4, max_position_embeddings=64),
     "gpt_oss": dict(model_type="gpt_oss", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                     rms_norm_eps=1e-5, num_local_experts=8, num_experts_per_tok=2, intermediate_size=32,
                     swiglu_limit=7.0, sliding_window=4, attention_bias=True,

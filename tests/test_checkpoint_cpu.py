@@ -24,7 +24,7 @@ def test_reshard_roundtrip(tmp_path, save_layout, load_layout):
     launch(pp1 * ep1, checkpoint_worker.run, pp1, ep1, str(tmp_path), "load")
 
 
-@pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
+@pytest.mark.parametrize("model", ["deepseek", "gpt_oss", "qwen35"])
 def test_muon_state_roundtrip_other_families(tmp_path, model):
     """Muon momentum and AdamW moments of the MLA / shared-expert / dense-first-layer model and of the model with
     expert biases survive a save at pp2·ep2 and a load at pp1·ep2 (pithtrain tests/test_muon_checkpoint.py:109-125)."""

@@ -10,7 +10,7 @@ def test_qwen3_ladder(pp, ep):
     launch(pp * ep, dualpipev_worker.run, "qwen3", pp, ep, 2 * pp + 1)
 
 
-@pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
+@pytest.mark.parametrize("model", ["deepseek", "gpt_oss", "qwen35"])
 def test_other_models_pp2_ep2(model):
     launch(4, dualpipev_worker.run, model, 2, 2, 5)
 
