@@ -9,7 +9,7 @@ model: Any = None  # dualpipe.DualPipeV
 dataset: Any = None
 optimizers: tuple = ()
 schedulers: tuple = ()
-shard_groups: tuple = ()
-model_config: Any = None  # parallel.flat_shard.FlatShardGroup instances
+shard_groups: tuple = ()  # parallel.flat_shard.FlatShardGroup instances
+model_config: Any = None  # the parsed config.json (SimpleNamespace)
 
 step: int = 0

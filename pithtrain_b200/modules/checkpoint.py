@@ -204,10 +204,24 @@ def checkpoint_dir(save_location, step: int) -> Path:
     return Path(save_location, "torch-dcp", "step-%08d" % step)
 
 
+def is_complete(path: Path) -> bool:
+    """A DCP directory is complete once its ``.metadata`` exists: the coordinator writes it after every rank has
+    finished its shard files, so a save that was interrupted (job killed, disk full) leaves a directory without it."""
+    return Path(path, ".metadata").is_file()
+
+
 def latest_checkpoint(save_location) -> Optional[Path]:
+    """Newest complete ``step-*`` directory; incomplete ones are skipped (and reported) so that a job killed in the
+    middle of a save resumes from the checkpoint before it."""
     root = Path(save_location, "torch-dcp")
-    steps = sorted((p for p in root.glob("step-*") if p.is_dir()), key=lambda p: int(p.name.removeprefix("step-")))
-    return steps[-1] if steps else None
+    steps = sorted((p for p in root.glob("step-*") if p.is_dir() and p.name.removeprefix("step-").isdigit()),
+                   key=lambda p: int(p.name.removeprefix("step-")))
+    for p in reversed(steps):
+        if is_complete(p):
+            return p
+        if logging.stdout is not None:
+            logging.stdout.info("Skip incomplete checkpoint (no .metadata): %s" % p)
+    return None
 
 
 def _rng_state() -> torch.Tensor:
@@ -352,7 +366,12 @@ def load_training_checkpoint(cfg) -> Optional[Path]:
         return None
     out.info("Load checkpoint: %s" % path)
     t0 = time.monotonic()
-    load_into(path, training.model, training.optimizers, training.schedulers)
+    try:
+        load_into(path, training.model, training.optimizers, training.schedulers)
+    except Exception as e:
+        # a damaged shard file may already have overwritten part of the live state: never continue from here
+        raise RuntimeError(f"checkpoint {path} could not be read ({type(e).__name__}: {e}); move it away to resume "
+                           f"from an older one") from e
     rng = Path(path, "rng-rank-%05d.pt" % distributed.rank)
     if rng.exists():
         _set_rng_state(torch.load(rng, weights_only=True))

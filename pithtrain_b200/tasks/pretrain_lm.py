@@ -124,6 +124,11 @@ def clip_grad_norm_(model: Optional[nn.Module] = None, max_norm: float = 1.0, no
     return total
 
 
+# Dense bf16 tensor-core peak of one B200 (the vendor's 4.5 PFLOP/s figure is with 2:4 sparsity). The step line's
+# utilisation is quoted against this nominal number; measured sustained cuBLAS throughput on a 1 kW part is ~0.6 of it.
+NOMINAL_BF16_FLOPS = 2.25e15
+
+
 def model_flops_per_token(config, seq_len: int) -> float:
     """Training FLOPs per token: 6 x active matmul parameters (lm_head included, embedding lookup
     excluded) + causal attention 3 x 2*S*Hq*D per layer."""
@@ -241,6 +246,14 @@ def train_step(cfg: PretrainLMCfg) -> dict:
     metrics = {"step": training.step, "step_time": elapsed, "device_step_time": device_s,
                "gradient_norm": float(gradient_norm), "peak_gpu_memory": float(peak), "load_balance_loss": lb_loss,
                "tokens_per_second": t.global_batch_size * t.sequence_length / max(elapsed, 1e-9)}
+    mfu = None
+    if use_cuda:
+        try:
+            per_gpu = metrics["tokens_per_second"] / d.world_size
+            mfu = per_gpu * model_flops_per_token(training.model_config, t.sequence_length) / NOMINAL_BF16_FLOPS
+            metrics["mfu"] = mfu
+        except Exception:  # a model whose config lacks the fields of the FLOP count: no figure rather than no step
+            mfu = None
     if d.rank == 0:
         lr = schedulers[0].get_last_lr()[0] if schedulers else t.lr
         loss_v = float(loss) if loss is not None else float("nan")
@@ -254,6 +267,8 @@ def train_step(cfg: PretrainLMCfg) -> dict:
                   "peak-gpu-memory %.2f GB" % metrics["peak_gpu_memory"]]
         if device_ms is not None:
             parts.append("device-step-time %.3f sec" % device_s)
+        if mfu is not None:
+            parts.append("model-flops-utilization %.3f" % mfu)
         logging.stdout.info(" | ".join(parts))
         activate_wandb(cfg)
         if logging.wandb is not None:

@@ -91,3 +91,24 @@ def test_param_group_membership_survives_canonical_roundtrip():
         for f, v in entry.items():
             if torch.is_tensor(v):
                 assert torch.equal(again["state"][k][f].float(), v.float()), (k, f)
+
+
+def test_interrupted_save_is_skipped_on_resume(tmp_path):
+    """Host-side fault injection: a newer checkpoint directory without ``.metadata`` (what a save killed half-way
+    leaves behind) is ignored and the job resumes from the complete checkpoint before it; a complete directory whose
+    shard file was truncated makes the resume fail loudly instead of training on from a half-loaded state."""
+    from pithtrain_b200.modules.checkpoint import is_complete, latest_checkpoint
+
+    launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "save")
+    good = latest_checkpoint(tmp_path)
+    assert good is not None and good.name == "step-00000002" and is_complete(good)
+    partial = good.parent / "step-00000003"
+    partial.mkdir()
+    (partial / "__0_0.distcp").write_bytes(b"half a shard")
+    assert latest_checkpoint(tmp_path) == good
+    launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")  # asserts that it resumed at step 2
+
+    shard = sorted(good.glob("*.distcp"))[0]
+    shard.write_bytes(shard.read_bytes()[:64])
+    with pytest.raises(AssertionError, match="failed"):  # every rank exits non-zero; nobody trains on
+        launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")
