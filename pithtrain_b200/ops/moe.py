@@ -213,12 +213,11 @@ def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor, row_w: Optional[torch.Tenso
 
 def segment_sum(x: torch.Tensor, offs: torch.Tensor, num_groups: int) -> torch.Tensor:
     """Per-group column sums ``[G, H]`` in fp32 of rows ``[offs[g], offs[g+1])`` (bias gradients)."""
-    R = x.shape[0]
-    row = torch.arange(R, device=x.device)
-    gid = torch.bucketize(row, offs[1:].long(), right=True)  # rows past offs[-1] -> G
-    out = torch.zeros((num_groups + 1, x.shape[1]), dtype=torch.float32, device=x.device)
-    out.index_add_(0, gid, x.float())
-    return out[:num_groups]
+    # A segmented reduction over the sorted rows: one pass, no atomics, deterministic. (An ``index_add_`` by group id
+    # sends every element through an atomic on one of only ``G x H`` addresses — the pattern the reference measured
+    # at about half of the GPU time before its segmented-sum kernel, pithtrain/operators/indexed_bias_add.py:7-13.)
+    # Rows at or past ``offs[-1]`` belong to no group and are not read; ``unsafe`` skips the host-side length check.
+    return torch.segment_reduce(x.float(), "sum", offsets=offs[:num_groups + 1].long(), axis=0, unsafe=True)
 
 
 def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
