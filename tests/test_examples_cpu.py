@@ -1,0 +1,64 @@
+"""Every example script builds a valid configuration (nothing is launched): the config files exist, the mesh fits the
+model, the objects serialise, and the shell launchers parse."""
+import importlib.util
+import json
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+SCRIPTS = sorted((ROOT / "examples").glob("*/*/script.py"))
+
+
+def _load(path: Path):
+    spec = importlib.util.spec_from_file_location("example_" + path.parent.name.replace("-", "_").replace(".", "_") + "_" + path.parent.parent.name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)  # scripts launch only under __main__
+    return mod
+
+
+def test_examples_exist_for_every_model_and_task():
+    names = {(p.parent.parent.name, p.parent.name) for p in SCRIPTS}
+    models = {"deepseek-v2-lite", "qwen3-30b-a3b", "qwen3.5-35b-a3b", "gpt-oss-20b", "gpt-oss-120b"}
+    assert {("pretrain_lm", m) for m in models} <= names and {("convert_checkpoint", m) for m in models} <= names
+    assert len([n for n in names if n[0] == "tokenize_corpus"]) >= 4
+
+
+@pytest.mark.parametrize("script", SCRIPTS, ids=lambda p: f"{p.parent.parent.name}/{p.parent.name}")
+def test_example_builds_its_configuration(script):
+    from pithtrain_b200.config import SlottedDefault
+
+    mod = _load(script)
+    cfg = mod.make_cfg()
+    assert isinstance(cfg, SlottedDefault)
+    json.dumps(cfg.to_json_dict(), default=str)  # what the trainer logs at start-up
+    task = script.parent.parent.name
+    if task == "pretrain_lm":
+        from pithtrain_b200.dualpipe.dualpipev import layer_partition
+        from pithtrain_b200.modules.training import load_model_config, model_class_for
+
+        t, d = cfg.training, cfg.distributed
+        mc = load_model_config(t.model)
+        assert model_class_for(mc) is not None
+        pp, ep, cp = d.pipeline_parallel_size, d.expert_parallel_size, d.context_parallel_size
+        experts = getattr(mc, "num_experts", None) or getattr(mc, "n_routed_experts", None) or getattr(mc, "num_local_experts")
+        assert experts % ep == 0
+        assert all(len(layer_partition(mc.num_hidden_layers, 2 * pp, s)) >= 1 for s in range(2 * pp))
+        assert t.sequence_length % (2 * cp) == 0
+        # the smallest job the mesh allows still has 2·pp micro-batches per rank
+        assert t.global_batch_size % (t.micro_batch_size * ep) == 0
+        assert t.global_batch_size // (t.micro_batch_size * ep) >= 2 * pp
+        assert callable(t.optimizer) and callable(t.scheduler) and t.max_steps > 0
+    elif task == "convert_checkpoint":
+        assert cfg.operation in ("hf2dcp", "dcp2hf") and cfg.load_path and cfg.save_path
+    else:
+        assert cfg.tokenizer_name and cfg.source_path and cfg.output_path
+
+
+@pytest.mark.parametrize("launcher", sorted((ROOT / "examples").glob("*/launch.sh")) + [ROOT / "benchmarks" / "pretraining" / "launch.sh"],
+                         ids=lambda p: str(p.relative_to(ROOT)))
+def test_launchers_parse(launcher):
+    assert subprocess.run(["bash", "-n", str(launcher)]).returncode == 0
+    text = launcher.read_text()
+    assert "127.0.0.1" in text or "MASTER_ADDR" in text or "torchrun" not in text
