@@ -196,3 +196,16 @@ def test_memory_trace_follows_the_schedule(tmp_path, monkeypatch):
     out = tmp_path / "trace.json"
     launch(2, train_worker.run_memory_trace, str(out), timeout=300.0)
     assert json.load(open(out))["rows"] > 0
+
+
+def test_wandb_tracking_is_lazy_and_logs_the_metric_set(tmp_path):
+    import json
+
+    from utilities import launch
+
+    import train_worker
+
+    out = tmp_path / "wandb.json"
+    launch(1, train_worker.run_with_fake_wandb, str(out), timeout=300.0)
+    rows = json.load(open(out))
+    assert len(rows) == 2 and rows[0]["train/cross-entropy-loss"] > 0

@@ -169,3 +169,54 @@ def run_memory_trace(rank: int, world: int, out_path: str):
     assert trace.peak() is not None and torch.isfinite(torch.tensor(traced)) and plain > 0
     if rank == 0:
         json.dump({"rows": len(trace.rows)}, open(out_path, "w"))
+
+
+def run_with_fake_wandb(rank: int, world: int, out_path: str):
+    """Two steps with tracking configured and a stand-in ``wandb`` module: the run is created lazily after the first
+    good step, metrics are defined against ``train/step`` and every step logs the trainer's metric set."""
+    import json
+    import sys
+    import types
+
+    calls = {"init": [], "define": [], "log": []}
+
+    class Run:
+        def log(self, row):
+            calls["log"].append(dict(row))
+
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: (calls["init"].append({k: (v if k != "config" else sorted(v)) for k, v in kw.items()}), Run())[1]
+    fake.define_metric = lambda name, step_metric=None: calls["define"].append((name, step_metric))
+    sys.modules["wandb"] = fake
+
+    from pithtrain_b200.contexts import logging as log_ctx
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import LoggingWandbCfg, setup_logging
+    from pithtrain_b200.modules.training import make_adamw_optimizer, make_constant_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg, train_step
+
+    cfg = PretrainLMCfg()
+    t = cfg.training
+    t.model = dict(TINY_CPU, hidden_size=64, head_dim=16, moe_intermediate_size=32, vocab_size=128)
+    t.sequence_length, t.micro_batch_size, t.global_batch_size = 16, 1, 2
+    t.lr, t.max_steps, t.dataset = 1e-3, 2, None
+    t.moe_load_balance_coef, t.moe_load_balance_type = 1e-3, "micro-batch"
+    t.optimizer, t.scheduler = make_adamw_optimizer, make_constant_scheduler
+    t.param_dtype, t.grad_dtype = "fp32", "fp32"
+    w = LoggingWandbCfg()
+    w.entity, w.project, w.name, w.group = "team", "proj", "tiny", "ci"
+    cfg.logging.wandb = w
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    assert log_ctx.wandb is None and not calls["init"]  # nothing is created before a step has succeeded
+    train_step(cfg)
+    train_step(cfg)
+    assert len(calls["init"]) == 1 and calls["init"][0]["entity"] == "team" and calls["init"][0]["name"] == "tiny"
+    assert all(step == "train/step" for _, step in calls["define"]) and len(calls["define"]) >= 6
+    assert len(calls["log"]) == 2 and [r["train/step"] for r in calls["log"]] == [0, 1]
+    keys = set(calls["log"][0])
+    assert {"train/cross-entropy-loss", "train/load-balance-loss", "train/learning-rate", "train/gradient-norm",
+            "infra/tokens-per-second", "infra/peak-gpu-memory", "infra/step-time"} <= keys
+    assert calls["log"][0]["train/load-balance-loss"] > 0
+    json.dump(calls["log"], open(out_path, "w"))
