@@ -69,6 +69,11 @@ def comm_buffer_bytes(dims: ModelDims, par: ParallelCfg, tc: TokenCounts) -> int
         n += 4 * cells * dims.H * 2 + 2 * cells * dims.k * 8
     if par.pp > 1:
         n += 4 * tc.T * dims.H * 2  # activations / gradients in flight in each direction
+    if par.cp > 1:
+        # context-parallel payload exchange (one per payload shape, shared by all layers): two slots of the published
+        # K/V (or MLA latent + rope key) in bf16, and two slots of cp per-writer gradient partitions in fp32
+        per_token = (dims.kv_lora + dims.d_rope) if dims.kv_lora else dims.nkv * (dims.d_qk + dims.d_v)
+        n += 2 * tc.T * per_token * 2 + 2 * par.cp * tc.T * per_token * 4
     return n
 
 

@@ -78,3 +78,20 @@ def test_fp8_training_adds_both_weight_orientations():
     assert 28.0 < extra < 29.5, extra
     experts = 48 * 64 * 3 * 2048 * 768
     assert fp8.fp8_weights > 2 * experts  # experts dominate; attention projections come on top
+
+
+def test_context_parallel_exchange_buffers_are_counted():
+    from pathlib import Path
+
+    from pithtrain_b200.tools.memory_estimator.activation_profile import token_counts
+    from pithtrain_b200.tools.memory_estimator.model_profile import ModelDims, ParallelCfg
+    from pithtrain_b200.tools.memory_estimator.schedule_simulator import comm_buffer_bytes
+
+    root = Path(__file__).resolve().parents[1] / "examples" / "pretrain_lm"
+    for name, per_token in (("gpt-oss-20b", 8 * (64 + 64)), ("deepseek-v2-lite", 512 + 64)):
+        dims = ModelDims.from_json(str(root / name / "config.json"))
+        one = ParallelCfg(cp=1, sequence_length=32768, global_batch_size=4)
+        four = ParallelCfg(cp=4, sequence_length=32768, global_batch_size=4)
+        extra = comm_buffer_bytes(dims, four, token_counts(dims, four, 1.0)) - comm_buffer_bytes(dims, one, token_counts(dims, one, 1.0))
+        T = 32768 // 4
+        assert extra == 2 * T * per_token * 2 + 2 * 4 * T * per_token * 4, (name, extra)
