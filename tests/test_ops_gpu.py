@@ -331,3 +331,25 @@ def test_own_causal_attention_forward(B, S, Hq, Hkv):
     ref, ref_lse = attention_ref(q, k, v, causal=True, return_lse=True)
     assert calc_diff(out.float(), ref.float()) < 1e-3
     assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.skipif(os.environ.get("PITHTRAIN_NS_GEMM", "library") != "own",
+                    reason="Newton-Schulz on the own grouped GEMMs runs only with PITHTRAIN_NS_GEMM=own until it is timed")
+@pytest.mark.parametrize("shape", [(8, 768, 2048), (4, 2048, 768), (1, 512, 2048), (2048, 4096)])
+def test_newton_schulz_on_own_gemms_matches_library_products(shape):
+    from pithtrain_b200.modules.optimizer import newtonschulz5_own_gemm
+
+    torch.manual_seed(12)
+    G = torch.randn(*shape, device="cuda").bfloat16()
+    got = newtonschulz5_own_gemm(G).float()
+    torch.cuda.synchronize()
+    _native.check_status()
+    os.environ["PITHTRAIN_NS_GEMM"] = "library"
+    try:
+        from pithtrain_b200.modules.optimizer import zeropower_via_newtonschulz5
+
+        want = zeropower_via_newtonschulz5(G).float()
+    finally:
+        os.environ["PITHTRAIN_NS_GEMM"] = "own"
+    assert got.shape == want.shape
+    assert float((got - want).norm() / want.norm()) < 0.05
