@@ -314,6 +314,53 @@ def _collect_garbage() -> None:
 # ------------------------------------------------------------------------------------------------
 # checkpoints (thin wrappers; the format lives in modules.checkpoint)
 # ------------------------------------------------------------------------------------------------
+class AppState:
+    """The ``app`` entry of a checkpoint as one object with ``state_dict`` / ``load_state_dict`` (the protocol of
+    ``torch.distributed.checkpoint.stateful.Stateful``), for callers that drive ``dcp.save`` / ``dcp.load`` themselves.
+
+    ``state_dict`` returns canonical (mesh-independent) keys: ``model`` without the ``module.N.`` prefix and with one
+    entry per global expert, ``optimizer`` keyed the same way, ``scheduler`` as a list; with ``model_only`` just the
+    model (what a checkpoint converted from Hugging Face holds). ``load_state_dict`` maps canonical keys back onto
+    whatever this rank owns and skips optimizer and scheduler entries that are absent. Same role as the reference's
+    class of this name (pithtrain/tasks/pretrain_lm.py:156-220); ``save_checkpoint`` / ``load_checkpoint`` below use
+    the functions of ``modules.checkpoint`` directly.
+    """
+
+    def __init__(self, model: nn.Module, optimizers=(), schedulers=(), model_only: bool = False) -> None:
+        self.model, self.optimizers, self.schedulers, self.model_only = model, tuple(optimizers), tuple(schedulers), model_only
+
+    def state_dict(self) -> dict:
+        from ..modules import checkpoint as ckpt
+
+        model_state = ckpt.to_canonical_model(dict(self.model.state_dict()), self.model)
+        if self.model_only:
+            return {"model": model_state}
+        return {"model": model_state, "optimizer": ckpt.to_canonical_optim(self.optimizers, self.model),
+                "scheduler": [s.state_dict() for s in self.schedulers]}
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        from ..modules import checkpoint as ckpt
+
+        local = ckpt.to_localized_model(state_dict["model"], self.model)
+        with torch.no_grad():
+            own = self.model.state_dict()
+            for k, v in local.items():
+                own[k].copy_(v)  # in place: parameters are views into flat buffers
+        optim = state_dict.get("optimizer")
+        if optim and self.optimizers:
+            if torch.is_tensor(optim.get("param_groups")):
+                optim = dict(optim, param_groups=ckpt._from_blob(optim["param_groups"]))
+            ckpt.to_localized_optim(optim, self.model, self.optimizers)
+        sched = state_dict.get("scheduler")
+        if torch.is_tensor(sched):
+            sched = ckpt._from_blob(sched)
+        if sched:
+            if isinstance(sched, dict):  # a checkpoint written with a single scheduler
+                sched = [sched]
+            for s, st in zip(self.schedulers, sched):
+                s.load_state_dict(st)
+
+
 def save_checkpoint(cfg: PretrainLMCfg) -> None:
     from ..modules import checkpoint as ckpt
 

@@ -112,3 +112,9 @@ def test_interrupted_save_is_skipped_on_resume(tmp_path):
     shard.write_bytes(shard.read_bytes()[:64])
     with pytest.raises(AssertionError, match="failed"):  # every rank exits non-zero; nobody trains on
         launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")
+
+
+def test_app_state_roundtrip_in_one_process():
+    import train_worker
+
+    launch(1, train_worker.run_app_state_roundtrip, timeout=300.0)

@@ -220,3 +220,61 @@ def run_with_fake_wandb(rank: int, world: int, out_path: str):
             "infra/tokens-per-second", "infra/peak-gpu-memory", "infra/step-time"} <= keys
     assert calls["log"][0]["train/load-balance-loss"] > 0
     json.dump(calls["log"], open(out_path, "w"))
+
+
+def run_app_state_roundtrip(rank: int, world: int):
+    """AppState of a trained tiny model loads into a freshly built, perturbed one: parameters, optimizer
+    state and scheduler position are equal afterwards and the next step produces the same loss."""
+    import copy
+
+    import torch
+
+    from pithtrain_b200.contexts import training
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import make_muon_optimizer, make_wsd_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import AppState, PretrainLMCfg, train_step
+    from functools import partial
+
+    def make(seed):
+        cfg = PretrainLMCfg()
+        t = cfg.training
+        t.model = dict(TINY_CPU, hidden_size=64, head_dim=16, moe_intermediate_size=32, vocab_size=128)
+        t.sequence_length, t.micro_batch_size, t.global_batch_size = 16, 1, 2
+        t.lr, t.max_steps, t.dataset, t.seed = 1e-2, 8, None, seed
+        t.optimizer, t.scheduler = make_muon_optimizer, partial(make_wsd_scheduler, warmup_ratio=0.5)
+        t.param_dtype, t.grad_dtype = "fp32", "fp32"
+        return cfg
+
+    cfg = make(1234)
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    train_step(cfg)
+    train_step(cfg)
+    saved = copy.deepcopy(AppState(training.model, training.optimizers, training.schedulers).state_dict())
+    assert set(saved) == {"model", "optimizer", "scheduler"}
+    assert all(not k.startswith("module.") for k in saved["model"])
+    assert any(".experts.7." in k for k in saved["model"]) and not any(k.endswith("experts.gate_proj.weight") for k in saved["model"])
+    assert set(AppState(training.model, model_only=True).state_dict()) == {"model"}
+    want = train_step(cfg)["loss"]
+
+    cfg2 = make(1234)  # same seed: the synthetic token stream is a function of it
+    setup_training(cfg2)
+    with torch.no_grad():
+        for p in training.model.parameters():
+            p.add_(torch.randn_like(p) * 0.01)  # a different starting point than the saved run had
+    fresh = AppState(training.model, training.optimizers, training.schedulers)
+    assert any(not torch.equal(v, saved["model"][k]) for k, v in fresh.state_dict()["model"].items())
+    fresh.load_state_dict(saved)
+    again = fresh.state_dict()
+    for k, v in saved["model"].items():
+        assert torch.equal(again["model"][k], v), k
+    for k, entry in saved["optimizer"]["state"].items():
+        for f, v in entry.items():
+            if torch.is_tensor(v):
+                assert torch.allclose(again["optimizer"]["state"][k][f].float(), v.float()), (k, f)
+    assert training.schedulers[0].get_last_lr() == [saved["scheduler"][0]["_last_lr"][0]]
+    training.step = 2
+    got = train_step(cfg2)["loss"]
+    assert abs(got - want) < 1e-5 * abs(want), (got, want)
