@@ -20,6 +20,7 @@ from typing import Optional, Tuple
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+from torch.distributed.elastic.multiprocessing.errors import record
 
 from ..config import SlottedDefault
 from ..contexts import distributed, logging, training
@@ -384,9 +385,11 @@ def raise_if_dataset_insufficient(cfg: PretrainLMCfg) -> None:
         raise SystemExit(1)
 
 
+@record
 def launch(cfg: PretrainLMCfg) -> None:
     """Entry point of the task: set up logging, distributed runtime and training state, resume from the
-    newest checkpoint if there is one, and train."""
+    newest checkpoint if there is one, and train. ``@record`` hands an uncaught exception to torchrun's error file,
+    so the launcher's summary names the failing rank and its traceback (pithtrain/tasks/pretrain_lm.py:496)."""
     setup_logging(cfg)
     setup_distributed(cfg)
     setup_training(cfg)
