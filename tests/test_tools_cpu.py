@@ -209,3 +209,17 @@ def test_wandb_tracking_is_lazy_and_logs_the_metric_set(tmp_path):
     launch(1, train_worker.run_with_fake_wandb, str(out), timeout=300.0)
     rows = json.load(open(out))
     assert len(rows) == 2 and rows[0]["train/cross-entropy-loss"] > 0
+
+
+def test_tiny_cpu_benchmark_script_prints_its_json_line():
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    res = subprocess.run([sys.executable, str(root / "benchmarks" / "pretraining" / "tiny_cpu.py"), "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    row = json.loads(res.stdout.strip().splitlines()[-1])
+    assert row["unit"] == "ms" and row["value"] > 0 and row["higher_is_better"] is False and 6.0 < row["final_loss"] < 7.5
