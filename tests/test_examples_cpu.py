@@ -62,3 +62,23 @@ def test_launchers_parse(launcher):
     assert subprocess.run(["bash", "-n", str(launcher)]).returncode == 0
     text = launcher.read_text()
     assert "127.0.0.1" in text or "MASTER_ADDR" in text or "torchrun" not in text
+
+
+def test_greedy_decode_example_runs_on_a_tiny_model(tmp_path):
+    """The inference example end to end on CPU: a tiny config written to disk, random weights, a few new tokens."""
+    import os
+    import sys
+
+    cfg = dict(model_type="qwen3_moe", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+               rms_norm_eps=1e-6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
+               vocab_size=96, num_hidden_layers=2, max_position_embeddings=64, rope_theta=1e6, attention_bias=False)
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(cfg))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", RANK="0", WORLD_SIZE="1",
+               LOCAL_RANK="0", PITHTRAIN_NO_FAILFAST="1")
+    res = subprocess.run([sys.executable, str(ROOT / "examples" / "inference" / "greedy_decode.py"), "--model", str(path),
+                          "--prompt-ids", "5,6,7", "--new-tokens", "3", "--seq", "16"], capture_output=True, text=True,
+                         timeout=300, env=env)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    out = res.stdout + res.stderr
+    assert "5, 6, 7" in out or "[5, 6, 7" in out or "5,6,7" in out, out[-800:]
