@@ -1,5 +1,8 @@
 """Developer tools: log comparison."""
 import pytest
+from pathlib import Path
+
+ROOT_DIR = Path(__file__).resolve().parents[1]
 from pithtrain_b200.tools.validate_correctness import compare
 
 LINE = ("[2026-01-01 00:00:0{i}] step 0000000{i}/00000025 | step-time {t} sec | cross-entropy-loss {ce} | "
@@ -223,3 +226,18 @@ def test_tiny_cpu_benchmark_script_prints_its_json_line():
     assert res.returncode == 0, res.stderr[-2000:]
     row = json.loads(res.stdout.strip().splitlines()[-1])
     assert row["unit"] == "ms" and row["value"] > 0 and row["higher_is_better"] is False and 6.0 < row["final_loss"] < 7.5
+
+
+def test_validation_run_recipes_build():
+    from argparse import Namespace
+
+    from pithtrain_b200.tools.validate_correctness.validate import RECIPES, make_cfg
+
+    for model in RECIPES:
+        a = Namespace(model=model, pipeline_parallel_size=2, expert_parallel_size=4, context_parallel_size=1, synthetic=True,
+                      max_steps=25, global_batch_size=1024, sequence_length=2048, fp8=False, num_hidden_layers=0)
+        cfg = make_cfg(a)
+        t = cfg.training
+        assert t.dataset is None and t.lr == 1e-6 and t.max_steps == 25 and t.model.name == "config.json"
+        assert (ROOT_DIR / t.model).exists(), t.model
+        assert t.moe_load_balance_type in ("sequence", "global-batch", "micro-batch")
