@@ -15,6 +15,8 @@ dense ``nn.Linear`` calls.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native
@@ -57,11 +59,29 @@ def _chk2d(t: torch.Tensor, name: str):
     assert t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0, f"{name} must be 16-byte aligned"
 
 
+# Opt-in: plain dense NT products go to the 2-CTA kernel of csrc/gemm_2cta.cu (not validated on hardware yet).
+USE_2CTA = os.environ.get("PITHTRAIN_GEMM_2CTA", "0") == "1"
+
+
+def _gemm2cta_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    rc = _native.lib().pt_gemm2cta_nt(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+                                      out.stride(0), _native.stream_ptr())
+    _native.check(rc, "pt_gemm2cta_nt")
+    return out
+
+
 @torch.no_grad()
 def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
             accumulate: bool = False, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x[M,K] @ w[N,K].T -> [M,N]``."""
     out_dtype = out_dtype or x.dtype
+    if (USE_2CTA and out is None and not accumulate and out_dtype == torch.bfloat16 and _native_ok(x, w)
+            and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0):
+        _chk2d(x, "x"); _chk2d(w, "w")
+        return _gemm2cta_nt(x, w)
     if not _native_ok(x, w):
         r = x.float() @ w.float().t()
         if out is None:

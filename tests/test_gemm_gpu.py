@@ -1,4 +1,5 @@
 """tcgen05 GEMM family vs fp32 PyTorch references (dense NT/NN/TN, M-grouped, K-grouped)."""
+import os
 import pytest
 import torch
 
@@ -163,3 +164,19 @@ def test_grouped_gather_matches_explicit_gather(sizes, N, K):
     _native.check_status()
     last = int(offs[-1])
     assert torch.equal(out2[:last], ref2[:last])
+
+
+@pytest.mark.skipif(os.environ.get("PITHTRAIN_GEMM_2CTA", "0") != "1",
+                    reason="the cta_group::2 GEMM runs only with PITHTRAIN_GEMM_2CTA=1 until it is validated")
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (4096, 5120, 2048), (300, 200, 136)])
+def test_two_cta_gemm_nt(M, N, K):
+    from pithtrain_b200.ops import gemm as G
+
+    torch.manual_seed(21)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    got = G._gemm2cta_nt(x, w).float()
+    torch.cuda.synchronize()
+    _native.check_status()
+    ref = x.float() @ w.float().t()
+    assert calc_diff(got, ref) < 1e-4
