@@ -217,7 +217,8 @@ def segment_sum(x: torch.Tensor, offs: torch.Tensor, num_groups: int) -> torch.T
     # sends every element through an atomic on one of only ``G x H`` addresses — the pattern the reference measured
     # at about half of the GPU time before its segmented-sum kernel, pithtrain/operators/indexed_bias_add.py:7-13.)
     # Rows at or past ``offs[-1]`` belong to no group and are not read; ``unsafe`` skips the host-side length check.
-    return torch.segment_reduce(x.float(), "sum", offsets=offs[:num_groups + 1].long(), axis=0, unsafe=True)
+    o = offs[:num_groups + 1].long()
+    return torch.segment_reduce(x.float(), "sum", lengths=o[1:] - o[:-1], axis=0, unsafe=True)
 
 
 def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
