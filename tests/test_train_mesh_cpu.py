@@ -58,3 +58,9 @@ def test_other_families_under_context_parallel(tmp_path, model, world, ep, cp):
 
 def test_tiny_cpu_configuration_one_step():
     launch(1, train_worker.run_tiny_cpu_step, timeout=300.0)
+
+
+def test_benchmark_mode_balances_the_experts(tmp_path):
+    out = tmp_path / "bench_mode.json"
+    launch(2, train_worker.run_benchmark_mode, str(out), timeout=300.0)
+    assert len(json.load(open(out))) == 2

@@ -278,3 +278,34 @@ def run_app_state_roundtrip(rank: int, world: int):
     training.step = 2
     got = train_step(cfg2)["loss"]
     assert abs(got - want) < 1e-5 * abs(want), (got, want)
+
+
+def run_benchmark_mode(rank: int, world: int, out_path: str):
+    """``benchmark=True`` (the reference's throughput protocol): routing is replaced by a round-robin assignment, so
+    every expert receives the same number of rows and the load-balance metric is exactly 1."""
+    import json
+    import math
+
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import make_muon_optimizer, make_constant_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg, train_step
+
+    cfg = PretrainLMCfg()
+    cfg.distributed.expert_parallel_size = world
+    t = cfg.training
+    t.model = dict(TINY_CPU, hidden_size=64, head_dim=16, moe_intermediate_size=32, vocab_size=128)
+    t.sequence_length, t.micro_batch_size, t.global_batch_size = 32, 1, 2 * world
+    t.lr, t.max_steps, t.dataset, t.benchmark = 1e-6, 2, None, True
+    t.moe_load_balance_type, t.moe_load_balance_coef = "global-batch", 1e-3
+    t.optimizer, t.scheduler = make_muon_optimizer, make_constant_scheduler
+    t.param_dtype, t.grad_dtype = "fp32", "fp32"
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    rows = [train_step(cfg) for _ in range(2)]
+    for m in rows:
+        assert math.isfinite(m["gradient_norm"]) and abs(m["load_balance_loss"] - 1.0) < 1e-3, m
+    if rank == 0:
+        assert all(math.isfinite(m["loss"]) for m in rows)
+        json.dump([m["load_balance_loss"] for m in rows], open(out_path, "w"))
