@@ -125,6 +125,8 @@ def main() -> int:
                     help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
     ap.add_argument("--fp8", action="store_true", help="not the headline run: forward/dgrad GEMMs in block-scaled e4m3 (dtype says so)")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
+    ap.add_argument("--routing", choices=["natural", "balanced"], default="natural",
+                    help="balanced = TrainingCfg.benchmark: the round-robin router replay of the reference's throughput recipes")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -165,6 +167,7 @@ def main() -> int:
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
     t.num_hidden_layers_override = args.layers
+    t.benchmark = args.routing == "balanced"
 
     setup_logging(cfg)
     setup_distributed(cfg, failfast=False)
@@ -250,7 +253,8 @@ def main() -> int:
                 "micro_batch": 1, "parallelism": f"pp{pp}xcp{cp}xep{ep}xdp{distributed.dp_size}",
                 "optimizer": "Muon (2-D/expert weights) + AdamW (rest), grad clip 1.0" if args.optimizer == "muon" else "AdamW",
                 "grad_accumulators": t.grad_dtype, "muon_momentum": t.muon_momentum_dtype + (f", {t.optimizer_device_state_gb:.0f} GiB resident + the rest in pinned host memory (streamed each step)" if t.offload_optimizer_state else ""),
-                "routing": "natural (seeded random-init gate)", "ep_transport": args.ep_backend,
+                "routing": ("natural (seeded random-init gate)" if args.routing == "natural"
+                            else "force-balanced round-robin replay (benchmark mode)"), "ep_transport": args.ep_backend,
                 "l2": "inputs larger than L2: every step streams >10 GB of parameters and activations, no explicit flush",
             },
             "clocks": clocks,
