@@ -25,7 +25,6 @@ import subprocess
 import sys
 import threading
 import time
-from functools import partial
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent

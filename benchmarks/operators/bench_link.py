@@ -8,7 +8,6 @@ next to the 770 GB/s per direction measured for a plain peer copy on this pool a
 """
 
 import argparse
-import os
 import sys
 from pathlib import Path
 from types import SimpleNamespace

@@ -10,7 +10,7 @@ executor posts between two compute actions and commits them as one ``batch_isend
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

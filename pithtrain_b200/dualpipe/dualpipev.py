@@ -26,7 +26,7 @@ from . import comm
 from .execution import ChunkRecord, ExecutionCtx, model_backward, model_forward, nvtx_range
 from .overlap import overlapped_forward_backward
 from .schedule import Action, backward_dst, backward_src, build_schedule, forward_dst, forward_src
-from .utils import FP8WeightCacheControl, WeightGradStore, gather, scatter
+from .utils import FP8WeightCacheControl, WeightGradStore, scatter
 
 
 def layer_partition(num_layers: int, stage_count: int, stage_index: int) -> range:

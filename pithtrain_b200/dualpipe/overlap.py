@@ -16,7 +16,7 @@ cover unequal layer counts and dense layers without special cases.
 
 from __future__ import annotations
 
-from typing import Callable, Generator, List, Optional
+from typing import Callable, Generator, List
 
 import torch
 

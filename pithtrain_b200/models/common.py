@@ -6,7 +6,7 @@ stage-1/3/5 split, and the base class that turns a list of decoder layers into a
 from __future__ import annotations
 
 import math
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Any, Callable, Optional, Tuple
 
 import torch
 import torch.nn as nn

@@ -9,7 +9,7 @@ supports neither context parallelism nor packed sequences.
 
 from __future__ import annotations
 
-from typing import Any, Optional
+from typing import Any
 
 import torch
 import torch.nn as nn

@@ -21,7 +21,7 @@ than the parameter) and ``p.grad`` otherwise, and skip parameters this rank does
 
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 

@@ -10,7 +10,6 @@ FlashAttention-4 wrapper (pithtrain/operators/flash_attn_v4.py:17-99): ``causal`
 
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

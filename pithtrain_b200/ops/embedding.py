@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .common import accumulate_grad, grad_buffer
+from .common import grad_buffer
 from .moe import gather_rows
 
 

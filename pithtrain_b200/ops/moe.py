@@ -21,7 +21,7 @@ wgrad.
 from __future__ import annotations
 
 import os
-from typing import Callable, Optional, Tuple
+from typing import Callable, Optional
 
 import torch
 

@@ -19,8 +19,7 @@ reference refuses sinks and windows under context parallelism (pithtrain/models/
 
 from __future__ import annotations
 
-import math
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from .. import _native
-from .common import accumulate_colsum, accumulate_grad, sp, use_native
+from .common import accumulate_colsum, sp, use_native
 
 
 def rotate_half(x):

@@ -20,10 +20,9 @@ library's status word instead of corrupting memory.
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Optional, Tuple
+from typing import Dict, Tuple
 
 import torch
-import torch.distributed as dist
 
 from .. import _native
 from ..ops.moe import combine_rows

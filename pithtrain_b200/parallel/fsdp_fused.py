@@ -18,7 +18,7 @@ the library's status word. All ranks of the group must be on one node with peer 
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Tuple
+
 
 import torch
 import torch.distributed as dist
