@@ -372,3 +372,31 @@ def test_newton_schulz_on_grouped_gemm_products_matches_batched(shape):
     U, _, Vh = torch.linalg.svd(G.float(), full_matrices=False)
     polar = U @ Vh
     assert float((got * polar).sum() / (got.norm() * polar.norm())) > 0.97
+
+
+def test_native_call_sites_match_the_signature_table():
+    """Every ``.pt_*(...)`` call in the Python sources names an entry of ``_native.SIGS`` and passes as many arguments
+    as the entry declares; the built library (when present) exports every entry. ctypes would otherwise only complain
+    when the call is reached, which for most of them is on a GPU."""
+    import ast
+    import ctypes
+
+    from pithtrain_b200 import _native
+
+    files = [p for root in ("pithtrain_b200", "benchmarks", "tests") for p in (ROOT / root).rglob("*.py")]
+    files += [ROOT / "bench.py", ROOT / "__graft_entry__.py"]
+    problems = []
+    for path in files:
+        for node in ast.walk(ast.parse(path.read_text())):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr.startswith("pt_")):
+                continue
+            name = node.func.attr
+            if name not in _native.SIGS:
+                problems.append(f"{path.name}:{node.lineno}: {name} is not in SIGS")
+            elif not any(isinstance(a, ast.Starred) for a in node.args) and len(node.args) != len(_native.SIGS[name]):
+                problems.append(f"{path.name}:{node.lineno}: {name} called with {len(node.args)} arguments, SIGS declares {len(_native.SIGS[name])}")
+    assert not problems, problems
+    lib = ROOT / "pithtrain_b200" / "_lib" / "libpithb200.so"
+    if lib.exists():
+        handle = ctypes.CDLL(str(lib))
+        assert not [n for n in _native.SIGS if not hasattr(handle, n)]
