@@ -400,3 +400,19 @@ def test_native_call_sites_match_the_signature_table():
     if lib.exists():
         handle = ctypes.CDLL(str(lib))
         assert not [n for n in _native.SIGS if not hasattr(handle, n)]
+
+
+def test_channel_struct_layouts_match_the_library():
+    """The ctypes mirrors of the channel structs that kernels take by value have the size the compiled library reports
+    (host-only functions, so the check runs without a GPU)."""
+    import ctypes
+
+    lib = ROOT / "pithtrain_b200" / "_lib" / "libpithb200.so"
+    if not lib.exists():
+        pytest.skip("native library not built")
+    handle = ctypes.CDLL(str(lib))
+    from pithtrain_b200.parallel.ep_fused import EpChanStruct
+    from pithtrain_b200.parallel.fsdp_fused import FsdpChanStruct
+
+    assert ctypes.sizeof(EpChanStruct) == handle.pt_ep_chan_struct_size()
+    assert ctypes.sizeof(FsdpChanStruct) == handle.pt_fsdp_chan_struct_size()
