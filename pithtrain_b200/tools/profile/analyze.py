@@ -28,7 +28,7 @@ from typing import Dict, Iterable, List, Tuple
 
 GPU_CATS = {"kernel", "gpu_memcpy", "gpu_memset"}
 CLASSES = [
-    ("communication", re.compile(r"nccl|pt_ep_|ep_push|ep_return|ep_receive|ep_wait|ep_ack|ep_plan|symm", re.I)),
+    ("communication", re.compile(r"nccl|pt_ep_|ep_push|ep_return|ep_receive|ep_wait|ep_ack|ep_plan|ep_compact|fsdp::|symm", re.I)),
     ("attention", re.compile(r"fmha|flash|sdpa|attn|cudnn", re.I)),
     ("gemm", re.compile(r"gemm|nvjet|cutlass|cublas|xmma|tcgen05", re.I)),
     ("optimizer", re.compile(r"muon|adamw|sumsq|axpby|newton", re.I)),

@@ -241,3 +241,25 @@ def test_validation_run_recipes_build():
         assert t.dataset is None and t.lr == 1e-6 and t.max_steps == 25 and t.model.name == "config.json"
         assert (ROOT_DIR / t.model).exists(), t.model
         assert t.moe_load_balance_type in ("sequence", "global-batch", "micro-batch")
+
+
+def test_profile_analyzer_classifies_the_framework_kernels():
+    from pithtrain_b200.tools.profile.analyze import classify
+
+    cases = {
+        "pt::ep_push_kernel(pt::EpChan, int, unsigned int, ...)": "communication",
+        "pt::ep_compact_kernel(pt::EpChan, int, int const*, ...)": "communication",
+        "pt::fsdp::reduce_scatter_kernel(pt::fsdp::Chan, ...)": "communication",
+        "pt::fsdp::wait_kernel(pt::fsdp::Chan, int, unsigned int, int*)": "communication",
+        "ncclDevKernel_SendRecv(ncclDevKernelArgsStorage<4096ul>)": "communication",
+        "void pt::gemm_bf16_kernel<256, true, true, false, true>(CUtensorMap_st, ...)": "gemm",
+        "pt::gemm2cta_kernel(CUtensorMap_st, CUtensorMap_st, CUtensorMap_st, pt::Gemm2Args)": "gemm",
+        "nvjet_tst_256x256_64x4_2x1_2cta_v_bx_NNT": "gemm",
+        "pt::attn_fwd_kernel(CUtensorMap_st, CUtensorMap_st, CUtensorMap_st, pt::AttnArgs)": "attention",
+        "cudnn_generated_fort_native_sdpa_sm100_flash_bprop_f16_knob_31_128x128x128": "attention",
+        "pt::muon_momentum_kernel(...)": "optimizer",
+        "pt::rmsnorm_fwd_kernel<8>(...)": "other",
+    }
+    for name, want in cases.items():
+        assert classify(name, "kernel") == want, (name, classify(name, "kernel"))
+    assert classify("Memcpy DtoD (Device -> Device)", "gpu_memcpy") == "memcpy"
