@@ -106,6 +106,7 @@ SIGS = {
     "pt_quant_blocks": "PIIIPPPPP",
     "pt_gemm_fp8": "PPPIIIILLLLPLPPIIIIP",
     "pt_attn_fwd_causal": "PPPPPIIIILLLLFP",
+    "pt_attn_fwd_block": "PPPPPIIIIILLLLFP",
     "pt_gemm2cta_nt": "PPPIIILLLP",
 }
 

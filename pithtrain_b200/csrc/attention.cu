@@ -35,7 +35,8 @@ constexpr int AT_P_BYTES = 2 * AT_TILE;
 constexpr float AT_RESCALE_LOG2 = 8.0f;         // tolerated growth of a row maximum before O is rescaled
 
 struct AttnArgs {
-  int B, S, Hq, Hkv;
+  int B, S, Sk, Hq, Hkv;  // S query tokens and Sk key tokens per batch entry
+  int causal;            // 1: self-attention with the causal mask (S == Sk); 0: every query sees every key (ring blocks)
   float scale_log2;  // softmax scale * log2(e)
   __nv_bfloat16* out;
   long long ldo;     // elements between consecutive tokens of out
@@ -70,8 +71,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (args.Hq / args.Hkv);
   const int q0 = qt * AT_BM;
-  const int n_kv = qt + 1;  // causal: key tiles 0..qt
+  const int n_kv = args.causal ? qt + 1 : args.Sk / AT_BN;  // causal: key tiles 0..qt
   const int row_base = b * args.S;
+  const int kv_base = b * args.Sk;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -107,7 +109,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j % AT_KSTAGES;
         const uint32_t ph = (j / AT_KSTAGES) & 1;
-        const int kv0 = row_base + j * AT_BN;
+        const int kv0 = kv_base + j * AT_BN;
         ok = mbar_wait_bounded(&k_empty[s], ph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
         if (!ok) break;
         mbar_expect_tx(&k_full[s], AT_K_BYTES);
@@ -200,7 +202,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!good) { ok = false; break; }
       tc_fence_after();
       const uint32_t tS = tS0 + lane_off + sb * AT_BN;
-      const bool diag = (j == qt);
+      const bool diag = args.causal && (j == qt);
       const int kpos0 = j * AT_BN;
       // pass 1: row maximum (log2 domain)
       float mx = -INFINITY;
@@ -319,19 +321,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 }  // namespace pt
 
-// q [B*S, Hq*128], k, v [B*S, Hkv*128] bf16 with row pitches ldq / ldk / ldv (elements); S a multiple of 128.
-PT_API int pt_attn_fwd_causal(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Hq, int Hkv,
-                              long long ldq, long long ldk, long long ldv, long long ldo, float scale, void* stream_) {
+namespace {
+int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Sk, int Hq, int Hkv,
+                    long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal, void* stream_) {
   using namespace pt;
-  if (S % AT_BM != 0 || Hq % Hkv != 0 || B <= 0) return -2;
+  if (S % AT_BM != 0 || Sk % AT_BN != 0 || Hq % Hkv != 0 || B <= 0 || (causal && S != Sk)) return -2;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   CUtensorMap tmQ, tmK, tmV;
-  const uint64_t rows = (uint64_t)B * S;
+  const uint64_t rows = (uint64_t)B * S, kv_rows = (uint64_t)B * Sk;
   if (encode_tmap_2d(&tmQ, q, TM_BF16, rows, (uint64_t)Hq * AT_D, ldq, 128, 64, TM_SW_128)) return -3;
-  if (encode_tmap_2d(&tmK, k, TM_BF16, rows, (uint64_t)Hkv * AT_D, ldk, 128, 64, TM_SW_128)) return -3;
-  if (encode_tmap_2d(&tmV, v, TM_BF16, rows, (uint64_t)Hkv * AT_D, ldv, 64, 64, TM_SW_128)) return -3;
+  if (encode_tmap_2d(&tmK, k, TM_BF16, kv_rows, (uint64_t)Hkv * AT_D, ldk, 128, 64, TM_SW_128)) return -3;
+  if (encode_tmap_2d(&tmV, v, TM_BF16, kv_rows, (uint64_t)Hkv * AT_D, ldv, 64, 64, TM_SW_128)) return -3;
   AttnArgs a;
-  a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv;
+  a.B = B; a.S = S; a.Sk = Sk; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.out = static_cast<__nv_bfloat16*>(out); a.ldo = ldo;
   a.lse = static_cast<float*>(lse);
@@ -345,4 +347,20 @@ PT_API int pt_attn_fwd_causal(const void* q, const void* k, const void* v, void*
   dim3 grid(S / AT_BM, Hq, B);
   attn_fwd_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+}  // namespace
+
+// q [B*S, Hq*128], k, v [B*S, Hkv*128] bf16 with row pitches ldq / ldk / ldv (elements); S a multiple of 128.
+PT_API int pt_attn_fwd_causal(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Hq, int Hkv,
+                              long long ldq, long long ldk, long long ldv, long long ldo, float scale, void* stream_) {
+  return attn_fwd_launch(q, k, v, out, lse, B, S, S, Hq, Hkv, ldq, ldk, ldv, ldo, scale, 1, stream_);
+}
+
+// Block form for ring attention: S query tokens against Sk key tokens per batch entry, no mask. k and v may point
+// into another GPU's published buffer (plain, non-multicast TMA loads read it over NVLink), so the block can be
+// computed while it is being fetched instead of after a copy.
+PT_API int pt_attn_fwd_block(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Sk, int Hq,
+                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
+                             void* stream_) {
+  return attn_fwd_launch(q, k, v, out, lse, B, S, Sk, Hq, Hkv, ldq, ldk, ldv, ldo, scale, 0, stream_);
 }

@@ -7,7 +7,9 @@ registers a predicate and a function with the signatures below.
 The one implementation in the tree is the causal GQA forward of ``csrc/attention.cu`` (head dim 128, tcgen05 / TMEM,
 one softmax thread per row) with the library flash backward against the kernel's ``out`` and log-sum-exp. The
 kernel compiles but has not been validated on hardware yet, so it is registered only when
-``PITHTRAIN_OWN_ATTENTION=1`` is set; without the switch this module changes nothing.
+``PITHTRAIN_OWN_ATTENTION=1`` is set; without the switch this module changes nothing. ``PITHTRAIN_OWN_ATTENTION=ring``
+also lets ring attention hand the kernel the address of a peer's published K/V block (:func:`block_from_pointers`),
+so that the block is fetched by the kernel's own TMA loads while it is being consumed.
 """
 
 from __future__ import annotations
@@ -97,5 +99,27 @@ def causal_d128_attention(q, k, v, causal, scale, window_left, sinks, cu_seqlens
     return (out, lse) if return_lse else out
 
 
-if os.environ.get("PITHTRAIN_OWN_ATTENTION", "0") == "1":
+def block_from_pointers(q: torch.Tensor, k_ptr: int, v_ptr: int, Sk: int, Hkv: int, scale: float
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Unmasked attention of ``q [1, Sq, Hq, 128]`` against ``Sk`` keys/values stored token-major and contiguous
+    (``[Sk, Hkv, 128]`` bf16) at raw device addresses — which may lie in another GPU's published buffer: the kernel's
+    TMA loads then fetch the block over NVLink tile by tile while it computes. Returns fp32 ``out`` and ``lse``."""
+    from .. import _native
+
+    B, Sq, Hq, D = q.shape
+    assert B == 1 and D == 128 and q.dtype == torch.bfloat16 and Sq % 128 == 0 and Sk % 128 == 0 and _token_major(q)
+    out = torch.empty((1, Sq, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((1, Hq, Sq), dtype=torch.float32, device=q.device)
+    rc = _native.lib().pt_attn_fwd_block(q.data_ptr(), k_ptr, v_ptr, out.data_ptr(), lse.data_ptr(), 1, Sq, Sk, Hq, Hkv,
+                                         q.stride(1), Hkv * D, Hkv * D, out.stride(1), float(scale), _native.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"pt_attn_fwd_block failed with code {rc}")
+    return out.float(), lse
+
+
+MODE = os.environ.get("PITHTRAIN_OWN_ATTENTION", "0")
+# "1": causal self-attention on the own kernel; "ring": additionally, context-parallel steps read the peer's published
+# K/V in place through the block form of the kernel (ops/ring_attention.py) instead of copying the block first.
+RING_DIRECT = MODE == "ring"
+if MODE in ("1", "ring"):
     register(causal_d128_supported, causal_d128_attention)

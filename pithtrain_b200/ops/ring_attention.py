@@ -233,13 +233,14 @@ class _PeerPull:
     """Payload is published once in symmetric memory; step ``i`` reads rank ``rank - i`` directly, with the
     next step's block being fetched on a side stream meanwhile (pithtrain_b200/parallel/cp_fused.py)."""
 
-    def __init__(self, kind: str, payload, group, cp: int, rank: int, with_grads: bool):
+    def __init__(self, kind: str, payload, group, cp: int, rank: int, with_grads: bool, in_place: bool = False):
         from ..parallel.cp_fused import get_exchange
 
         self.cp, self.rank, self.local = cp, rank, payload
         self.ex = get_exchange(kind, group, cp, rank, payload, with_grads)
         self.epoch = self.ex.publish(payload)
         self.pending = None
+        self.in_place = in_place  # remote blocks are read where they were published: nothing is copied ahead
 
     def begin_step(self, i: int):
         if i == 0:
@@ -247,7 +248,8 @@ class _PeerPull:
         else:
             cur, ev = self.pending
             torch.cuda.current_stream().wait_event(ev)
-        self.pending = self.ex.pull((self.rank - i - 1) % self.cp, self.epoch) if i < self.cp - 1 else None
+        more = i < self.cp - 1 and not self.in_place
+        self.pending = self.ex.pull((self.rank - i - 1) % self.cp, self.epoch) if more else None
         return cur
 
     def end_step(self, i: int) -> None:
@@ -268,6 +270,20 @@ def _peer_pull_usable(group, cp: int, device) -> bool:
 
         _PULL_OK[key] = cp_fused.usable(group, cp, device)
     return _PULL_OK[key]
+
+
+def _in_place_blocks_usable(q: torch.Tensor, payload, expand, window_left: Optional[int]) -> bool:
+    """Remote K/V blocks can be consumed where their owner published them when the own attention kernel is enabled in
+    its ring mode and the case is the one it covers: plain K and V (no latent to expand), no window, one sequence per
+    micro-batch, head dim 128, bf16, blocks that are multiples of 128 tokens."""
+    from . import attention_native as N
+
+    if not N.RING_DIRECT or expand is not None or window_left is not None or len(payload) != 2:
+        return False
+    k, v = payload
+    B, S2, Hq, D = q.shape
+    return (B == 1 and D == 128 and k.shape[-1] == 128 and v.shape[-1] == 128 and q.dtype == torch.bfloat16
+            and k.dtype == torch.bfloat16 and (S2 // 2) % 128 == 0 and Hq % k.shape[2] == 0 and N._token_major(q[:, : S2 // 2]))
 
 
 def _pairs(cp: int, rank: int, src: int, block: int, window_left: Optional[int]):
@@ -294,9 +310,23 @@ class _RingAttention(torch.autograd.Function):
         lses: List[Optional[torch.Tensor]] = [None, None]
         start = [t.detach() for t in payload]
         pull = q.is_cuda and cp > 1 and _peer_pull_usable(group, cp, dev)
-        ring = _PeerPull("fwd", start, group, cp, rank, False) if pull else _NcclRing(start, group, cp, rank)
+        in_place = pull and _in_place_blocks_usable(q, start, expand, window_left)
+        ring = _PeerPull("fwd", start, group, cp, rank, False, in_place) if pull else _NcclRing(start, group, cp, rank)
         for i in range(cp):
             src = (rank - i) % cp
+            if in_place and i > 0:
+                # the attention kernel's own TMA loads fetch the remote block over NVLink while it computes
+                from . import attention_native as N
+
+                Hkv, D = start[0].shape[2], start[0].shape[3]
+                half = block * Hkv * D * start[0].element_size()
+                ring.ex.wait_ready(src, ring.epoch)
+                for qi, ki, rel, qb, kb in _pairs(cp, rank, src, block, None):
+                    assert rel == "full"  # without a window, blocks of other ranks are entirely visible or entirely not
+                    o_p, lse_p = N.block_from_pointers(q_halves[qi], ring.ex.peer_ptr(src, ring.epoch, 0) + ki * half,
+                                                       ring.ex.peer_ptr(src, ring.epoch, 1) + ki * half, block, Hkv, scale)
+                    outs[qi], lses[qi] = merge_partial(outs[qi], lses[qi], o_p, lse_p)
+                continue
             cur = ring.begin_step(i)
             with torch.no_grad():
                 k, v = expand(cur, params) if expand is not None else (cur[0], cur[1])

@@ -119,6 +119,15 @@ class PayloadExchange:
         ev.record(self.side)
         return out, ev
 
+    def wait_ready(self, src: int, epoch: int) -> None:
+        """Make the current stream wait (bounded) until ``src`` has published ``epoch``; kernels enqueued afterwards
+        may read ``src``'s slot in place through :meth:`peer_ptr`."""
+        self._wait(READY + src, 1, epoch, _native.stream_ptr())
+
+    def peer_ptr(self, src: int, epoch: int, j: int) -> int:
+        """Device address, valid in this process, of tensor ``j`` of the payload ``src`` published for ``epoch``."""
+        return self.buf.peer_ptrs[src] + (epoch & 1) * self.slot_bytes + self.offsets[j]
+
     def finish(self, epoch: int) -> None:
         """All pulls of ``epoch`` were consumed on the current stream: let owners reuse the slot."""
         torch.cuda.current_stream(self.device).wait_stream(self.side)
