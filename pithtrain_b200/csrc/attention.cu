@@ -1,4 +1,5 @@
-// Causal GQA attention forward for sm_100a, head dim 128, bf16 (tcgen05 / TMEM / TMA).
+// GQA attention forward for sm_100a, head dim 128, bf16 (tcgen05 / TMEM / TMA): causal self-attention, and the
+// unmasked block form that ring attention uses (K/V may then live in another GPU's published buffer).
 //
 // Status: compiles for sm_100a (63 registers, no spills) but has not been validated on hardware yet, so nothing
 // calls it unless PITHTRAIN_OWN_ATTENTION=1 is set (see ops/attention_native.py); the default attention path is the
