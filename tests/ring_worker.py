@@ -68,6 +68,22 @@ def _run_once(rank, world, case, device_type, first, seed):
         return
     Hq, Hkv, D = (4, 2, 8) if case != "mha" else (2, 2, 8)
     window = 5 if case == "window_sink" else None
+    if case == "gqa_d128_bf16":
+        # the shape family of the tcgen05 attention kernel: one sequence, head dim 128, blocks of 128 tokens, bf16
+        B, S, Hq, Hkv, D = 1, 256 * cp, 4, 2, 128
+        tol = 3e-3 if device_type == "cuda" else 1e-4
+        mk = lambda *shape: torch.randn(*shape).bfloat16()  # noqa: E731
+        q, k, v, go = mk(B, S, Hq, D), mk(B, S, Hkv, D), mk(B, S, Hkv, D), mk(B, S, Hq, D)
+        leaves = [t.float().requires_grad_() for t in (q, k, v)]
+        ref = attention_ref(leaves[0], leaves[1], leaves[2], causal=True)
+        ref.backward(go.float())
+        mine = [zigzag_slice(t, cp, r).clone().requires_grad_() for t in (q, k, v)]
+        out = ring_attention_func(mine[0], mine[1], mine[2])
+        out.backward(zigzag_slice(go, cp, r))
+        assert calc_diff(out.float(), zigzag_slice(ref.detach(), cp, r)) < tol
+        for a, b in zip(mine, leaves):
+            assert calc_diff(a.grad.float(), zigzag_slice(b.grad, cp, r)) < tol
+        return
     q, k, v = torch.randn(B, S, Hq, D), torch.randn(B, S, Hkv, D), torch.randn(B, S, Hkv, D)
     sinks = torch.randn(Hq) if case == "window_sink" else None
     go = torch.randn(B, S, Hq, D)
