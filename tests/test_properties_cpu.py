@@ -102,3 +102,23 @@ def test_zigzag_blocks_partition_the_sequence_and_balance_causal_work(cp, blocks
     assert flat == list(range(S))
     work = [sum(p + 1 for p in o) for o in owned]
     assert max(work) - min(work) == 0
+
+
+@FAST
+@given(m_tiles=st.integers(1, 40), n_tiles=st.integers(1, 40))
+def test_supergrouped_tile_order_visits_every_tile_once(m_tiles, n_tiles):
+    """The dense tile order of ``csrc/gemm.cu`` / ``csrc/gemm_2cta.cu`` (row tiles in supergroups of eight, so that CTAs
+    running together share A rows and B columns in L2), restated: linear index -> (row tile, column tile) is a
+    bijection."""
+    GROUP = 8
+    seen = set()
+    for t in range(m_tiles * n_tiles):
+        per = GROUP * n_tiles
+        gid = t // per
+        first_m = gid * GROUP
+        gsz = min(m_tiles - first_m, GROUP)
+        local = t - gid * per
+        mt, nt = first_m + local % gsz, local // gsz
+        assert 0 <= mt < m_tiles and 0 <= nt < n_tiles
+        seen.add((mt, nt))
+    assert len(seen) == m_tiles * n_tiles
