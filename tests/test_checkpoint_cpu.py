@@ -17,14 +17,14 @@ def test_canonical_keys():
         "layers.1.mlp.experts.6.gate_up_proj", "layers.1.mlp.experts.7.gate_up_proj"]
 
 
-@pytest.mark.parametrize("save_layout,load_layout", [((1, 1), (1, 1)), ((2, 2), (1, 4)), ((1, 2), (2, 1))])
+@pytest.mark.parametrize("save_layout,load_layout", [((2, 2), (1, 4)), ((1, 2), (2, 1))])
 def test_reshard_roundtrip(tmp_path, save_layout, load_layout):
     (pp0, ep0), (pp1, ep1) = save_layout, load_layout
     launch(pp0 * ep0, checkpoint_worker.run, pp0, ep0, str(tmp_path), "save")
     launch(pp1 * ep1, checkpoint_worker.run, pp1, ep1, str(tmp_path), "load")
 
 
-@pytest.mark.parametrize("model", ["deepseek", "gpt_oss", "qwen35"])
+@pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
 def test_muon_state_roundtrip_other_families(tmp_path, model):
     """Muon momentum and AdamW moments of the MLA / shared-expert / dense-first-layer model and of the model with
     expert biases survive a save at pp2·ep2 and a load at pp1·ep2 (pithtrain tests/test_muon_checkpoint.py:109-125)."""
