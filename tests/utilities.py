@@ -39,9 +39,26 @@ def _entry(rank: int, world: int, port: int, backend: str, fn: Callable, args: t
                 pass
 
 
+_FORKSERVER = None
+
+
+def _context(backend: str):
+    """CPU ranks are forked from a server process that has already imported torch (nothing else: no process group, no
+    threads), which saves the interpreter start-up and the torch import of every rank of every test; GPU ranks are
+    spawned, as CUDA wants."""
+    global _FORKSERVER
+    if backend != "gloo" or os.environ.get("PITHTRAIN_TEST_SPAWN", "0") == "1":
+        return mp.get_context("spawn")
+    if _FORKSERVER is None:
+        ctx = mp.get_context("forkserver")
+        ctx.set_forkserver_preload(["torch", "torch.distributed", "numpy"])
+        _FORKSERVER = ctx
+    return _FORKSERVER
+
+
 def launch(world: int, fn: Callable, *args, backend: str = "gloo", timeout: float = 240.0) -> None:
     """Run ``fn(rank, world, *args)`` in ``world`` processes; raises with the first failing rank's traceback."""
-    ctx = mp.get_context("spawn")
+    ctx = _context(backend)
     errq = ctx.SimpleQueue()
     port = free_port()
     procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn, args, errq)) for r in range(world)]
