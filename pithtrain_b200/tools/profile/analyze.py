@@ -3,8 +3,11 @@
     python -m pithtrain_b200.tools.profile.analyze workspace/profiles/qwen3 [--top 25] [--json out.json]
 
 Input: the ``trace_rank<r>.json[.gz]`` files written by ``capture`` (Chrome trace events; GPU work is every
-complete event of category ``kernel``, ``gpu_memcpy`` or ``gpu_memset`` and carries its stream id in ``args``).
-Per rank the tool reports
+complete event of category ``kernel``, ``gpu_memcpy`` or ``gpu_memset`` and carries its stream id in ``args``), or
+Nsight Systems exports (``nsys export --type=sqlite``; ``*.sqlite`` files, one per rank): kernels, copies and memsets
+come from the ``CUPTI_ACTIVITY_KIND_*`` tables, limited to the NVTX range that ``TrainingCfg.nsys_start`` opens
+(``rank=...``) when there is one, and every kernel is attributed to the engine's ``layerNN.stageK_{f,b,w}`` range that
+was open on the launching thread, which gives a per-stage table as well. Per rank the tool reports
 
 * the step window (first GPU event to last) and the time no stream was busy (launch- or host-bound gaps);
 * busy time per stream (union of its intervals) — the compute stream, the communication stream, copy streams;
@@ -55,6 +58,64 @@ def load_events(path: Path) -> List[dict]:
         if e.get("ph") == "X" and e.get("cat") in GPU_CATS and e.get("dur") is not None:
             out.append({"name": e.get("name", "?"), "cat": e["cat"], "ts": float(e["ts"]), "dur": float(e["dur"]),
                         "stream": (e.get("args") or {}).get("stream", e.get("tid", 0))})
+    return out
+
+
+STAGE_RX = re.compile(r"layer\d+\.(stage\d_[fbw])|^(prolog_[fb]|epilog_f|weight chunk|criterion|pipeline send/recv)$")
+
+
+def load_events_sqlite(path: Path) -> List[dict]:
+    """GPU work of one Nsight Systems export as the event dicts :func:`analyze_events` takes (times in microseconds);
+    events carry ``stage`` when the launch happened inside one of the engine's NVTX stage ranges."""
+    import bisect
+    import sqlite3
+
+    db = sqlite3.connect(f"file:{path}?mode=ro", uri=True)
+    tables = {r[0] for r in db.execute("SELECT name FROM sqlite_master WHERE type='table'")}
+    strings = dict(db.execute("SELECT id, value FROM StringIds")) if "StringIds" in tables else {}
+    out: List[dict] = []
+    if "CUPTI_ACTIVITY_KIND_KERNEL" in tables:
+        cols = {r[1] for r in db.execute("PRAGMA table_info(CUPTI_ACTIVITY_KIND_KERNEL)")}
+        name_col = "demangledName" if "demangledName" in cols else "shortName"
+        for start, end, stream, name_id, corr in db.execute(
+                f"SELECT start, end, streamId, {name_col}, correlationId FROM CUPTI_ACTIVITY_KIND_KERNEL"):
+            out.append({"name": strings.get(name_id, str(name_id)), "cat": "kernel", "ts": start / 1e3, "dur": (end - start) / 1e3,
+                        "stream": stream, "corr": corr})
+    for table, cat, label in (("CUPTI_ACTIVITY_KIND_MEMCPY", "gpu_memcpy", "Memcpy"), ("CUPTI_ACTIVITY_KIND_MEMSET", "gpu_memset", "Memset")):
+        if table in tables:
+            for start, end, stream, corr in db.execute(f"SELECT start, end, streamId, correlationId FROM {table}"):
+                out.append({"name": label, "cat": cat, "ts": start / 1e3, "dur": (end - start) / 1e3, "stream": stream, "corr": corr})
+    ranges = []  # (thread, start, end, text)
+    if "NVTX_EVENTS" in tables:
+        cols = {r[1] for r in db.execute("PRAGMA table_info(NVTX_EVENTS)")}
+        text = "COALESCE(n.text, s.value)" if "textId" in cols and strings else "n.text"
+        join = "LEFT JOIN StringIds s ON n.textId = s.id" if "textId" in cols and strings else ""
+        for start, end, tid, txt in db.execute(f"SELECT n.start, n.end, n.globalTid, {text} FROM NVTX_EVENTS n {join} WHERE n.end IS NOT NULL"):
+            if txt:
+                ranges.append((tid, start, end, txt))
+    window = [(s_, e_) for _, s_, e_, txt in ranges if txt.startswith("rank=")]
+    if window:
+        lo, hi = min(w[0] for w in window) / 1e3, max(w[1] for w in window) / 1e3
+        out = [e for e in out if e["ts"] >= lo and e["ts"] + e["dur"] <= hi]
+    if "CUPTI_ACTIVITY_KIND_RUNTIME" in tables and ranges:
+        launch = {corr: (tid, start) for corr, tid, start in db.execute("SELECT correlationId, globalTid, start FROM CUPTI_ACTIVITY_KIND_RUNTIME")}
+        per_thread: Dict[int, List[Tuple[int, int, str]]] = defaultdict(list)
+        for tid, start, end, txt in ranges:
+            m = STAGE_RX.search(txt)
+            if m:
+                per_thread[tid].append((start, end, m.group(1) or m.group(2)))
+        starts = {}
+        for tid in per_thread:
+            per_thread[tid].sort()
+            starts[tid] = [r[0] for r in per_thread[tid]]
+        for e in out:
+            tid, t = launch.get(e.get("corr"), (None, None))
+            if tid in per_thread:
+                # stage ranges of one thread do not nest: the candidate is the last one that started before the launch
+                i = bisect.bisect_right(starts[tid], t) - 1
+                if i >= 0 and per_thread[tid][i][1] >= t:
+                    e["stage"] = per_thread[tid][i][2]
+    db.close()
     return out
 
 
@@ -120,7 +181,20 @@ def analyze_events(events: List[dict], top: int = 25) -> Dict:
     classes = {c: {"sum_us": sum(e["dur"] for e in evs), "launches": len(evs)} for c, evs in by_class.items()}
     overlap = (intersect(comm, compute) / total(comm)) if comm and total(comm) > 0 else None
     ranked = sorted(by_name.items(), key=lambda kv: -sum(kv[1]))[:top]
-    return {"window_us": t1 - t0, "idle_us": (t1 - t0) - total(busy_all), "streams": streams, "classes": classes,
+    stages: Dict[str, Dict[str, float]] = {}
+    for e in events:
+        st = e.get("stage")
+        if st is None:
+            continue
+        row = stages.setdefault(st, {"sum_us": 0.0, "launches": 0, "comm_us": 0.0})
+        row["sum_us"] += e["dur"]
+        row["launches"] += 1
+        if e["cls"] == "communication":
+            row["comm_us"] += e["dur"]
+    for st, row in stages.items():
+        mine = union((e["ts"], e["ts"] + e["dur"]) for e in events if e.get("stage") == st and e["cls"] == "communication")
+        row["comm_overlap"] = (intersect(mine, compute) / total(mine)) if mine and total(mine) > 0 else None
+    return {"stages": stages, "window_us": t1 - t0, "idle_us": (t1 - t0) - total(busy_all), "streams": streams, "classes": classes,
             "comm_overlap": overlap, "comm_exposed_us": (total(comm) - intersect(comm, compute)) if comm else 0.0,
             "top": [{"name": n, "sum_us": sum(d), "launches": len(d), "mean_us": sum(d) / len(d)} for n, d in ranked]}
 
@@ -137,6 +211,11 @@ def render(rank: str, r: Dict) -> List[str]:
     if r["comm_overlap"] is not None:
         out.append(f"  communication overlapped with compute: {100 * r['comm_overlap']:.1f}% "
                    f"(exposed {r['comm_exposed_us'] / 1e3:.2f} ms)")
+    if r.get("stages"):
+        out.append("  stage (NVTX range at launch)   kernel ms  launches  communication ms  overlapped")
+        for st, v in sorted(r["stages"].items()):
+            ov = "-" if v["comm_overlap"] is None else f"{100 * v['comm_overlap']:.0f}%"
+            out.append(f"  {st:<30s}{v['sum_us'] / 1e3:10.2f}{v['launches']:10d}{v['comm_us'] / 1e3:18.2f}{ov:>12s}")
     out.append("  top kernels         sum ms  launches   mean us  name")
     for k in r["top"]:
         out.append(f"  {k['sum_us'] / 1e3:17.2f}{k['launches']:10d}{k['mean_us']:10.1f}  {k['name'][:100]}")
@@ -145,17 +224,19 @@ def render(rank: str, r: Dict) -> List[str]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("path", type=Path, help="trace file or directory of trace_rank*.json[.gz]")
+    ap.add_argument("path", type=Path, help="trace file (.json, .json.gz or an nsys .sqlite export) or a directory of them")
     ap.add_argument("--top", type=int, default=25)
     ap.add_argument("--json", type=Path, default=None)
     a = ap.parse_args(argv)
-    files = [a.path] if a.path.is_file() else sorted(list(a.path.glob("trace_rank*.json.gz")) + list(a.path.glob("trace_rank*.json")))
+    files = [a.path] if a.path.is_file() else sorted(list(a.path.glob("trace_rank*.json.gz")) + list(a.path.glob("trace_rank*.json"))
+                                                      + list(a.path.glob("*.sqlite")))
     if not files:
         print(f"no traces under {a.path}")
         return 1
     results = {}
     for f in files:
-        results[f.name.split(".")[0]] = analyze_events(load_events(f), a.top)
+        events = load_events_sqlite(f) if f.suffix == ".sqlite" else load_events(f)
+        results[f.name.split(".")[0]] = analyze_events(events, a.top)
     for rank, r in results.items():
         print("\n".join(render(rank, r)))
     if a.json:

@@ -263,3 +263,49 @@ def test_profile_analyzer_classifies_the_framework_kernels():
     for name, want in cases.items():
         assert classify(name, "kernel") == want, (name, classify(name, "kernel"))
     assert classify("Memcpy DtoD (Device -> Device)", "gpu_memcpy") == "memcpy"
+
+
+def test_profile_analyzer_reads_nsight_systems_sqlite_exports(tmp_path, capsys):
+    """A synthetic export with the tables the reader uses: kernels on a compute and a communication stream, launch
+    records, NVTX stage ranges and the ``rank=`` window opened by ``nsys_start``."""
+    import sqlite3
+
+    from pithtrain_b200.tools.profile import analyze as A
+
+    db_path = tmp_path / "rank0.sqlite"
+    db = sqlite3.connect(db_path)
+    db.executescript("""
+        CREATE TABLE StringIds (id INTEGER PRIMARY KEY, value TEXT);
+        CREATE TABLE CUPTI_ACTIVITY_KIND_KERNEL (start INT, end INT, deviceId INT, streamId INT, correlationId INT, demangledName INT, shortName INT);
+        CREATE TABLE CUPTI_ACTIVITY_KIND_MEMCPY (start INT, end INT, deviceId INT, streamId INT, correlationId INT, bytes INT, copyKind INT);
+        CREATE TABLE CUPTI_ACTIVITY_KIND_RUNTIME (start INT, end INT, globalTid INT, correlationId INT, nameId INT);
+        CREATE TABLE NVTX_EVENTS (start INT, end INT, eventType INT, text TEXT, globalTid INT, textId INT);
+    """)
+    names = {1: "void pt::gemm_bf16_kernel<256, false, false, false, false>(CUtensorMap_st)", 2: "pt::ep_push_kernel(pt::EpChan)",
+             3: "pt::rmsnorm_fwd_kernel<8>()", 4: "layer03.stage2_f"}
+    db.executemany("INSERT INTO StringIds VALUES (?, ?)", names.items())
+    us = 1000
+    # (start, end, stream, corr, name id): a GEMM on stream 7 overlapping a push on stream 9; one kernel before the window
+    kernels = [(100 * us, 200 * us, 7, 11, 1), (120 * us, 180 * us, 9, 12, 2), (210 * us, 220 * us, 7, 13, 3), (10 * us, 20 * us, 7, 14, 3)]
+    db.executemany("INSERT INTO CUPTI_ACTIVITY_KIND_KERNEL VALUES (?, ?, 0, ?, ?, ?, ?)", [(s, e, st, c, n, n) for s, e, st, c, n in kernels])
+    db.execute("INSERT INTO CUPTI_ACTIVITY_KIND_MEMCPY VALUES (?, ?, 0, 7, 15, 4096, 8)", (230 * us, 232 * us))
+    launches = [(95 * us, 11), (115 * us, 12), (205 * us, 13), (5 * us, 14), (228 * us, 15)]
+    db.executemany("INSERT INTO CUPTI_ACTIVITY_KIND_RUNTIME VALUES (?, ?, 42, ?, 0)", [(s, s + 2 * us, c) for s, c in launches])
+    nvtx = [(50 * us, 300 * us, "rank=0; pp=0/1 dp=0/1 cp=0/1 ep=0/2; mbs=1 seq=4096", None),
+            (90 * us, 110 * us, "layer03.stage1_f", None), (112 * us, 118 * us, None, 4), (200 * us, 209 * us, "layer03.stage3_f", None)]
+    db.executemany("INSERT INTO NVTX_EVENTS VALUES (?, ?, 59, ?, 42, ?)", nvtx)
+    db.commit()
+    db.close()
+
+    events = A.load_events_sqlite(db_path)
+    assert len(events) == 4  # the kernel before the rank= window is dropped
+    r = A.analyze_events(events)
+    assert abs(r["window_us"] - 132.0) < 1e-6
+    assert r["classes"]["gemm"]["sum_us"] == 100.0 and r["classes"]["communication"]["sum_us"] == 60.0
+    assert r["comm_overlap"] == 1.0  # the push ran entirely under the GEMM
+    assert set(r["stages"]) == {"stage1_f", "stage2_f", "stage3_f"}
+    assert r["stages"]["stage2_f"]["comm_us"] == 60.0 and r["stages"]["stage2_f"]["comm_overlap"] == 1.0
+    assert r["stages"]["stage1_f"]["sum_us"] == 100.0 and r["stages"]["stage3_f"]["launches"] == 1
+    assert A.main([str(tmp_path)]) == 0
+    out = capsys.readouterr().out
+    assert "stage2_f" in out and "communication overlapped with compute: 100.0%" in out
