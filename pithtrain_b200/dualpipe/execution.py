@@ -32,9 +32,17 @@ from .utils import WeightGradStore, run_backward
 # ------------------------------------------------------------------------------------------------
 # NVTX (no-op without CUDA)
 # ------------------------------------------------------------------------------------------------
+# Set by the step-profile capture tool: ranges then also become profiler annotations, so that a trace can attribute
+# kernels to pipeline stages (NVTX ranges themselves are only visible to Nsight Systems).
+RECORD_RANGES = False
+
+
 @contextmanager
 def nvtx_range(name: str):
-    if torch.cuda.is_available():
+    if RECORD_RANGES:
+        with torch.profiler.record_function(name):
+            yield
+    elif torch.cuda.is_available():
         torch.cuda.nvtx.range_push(name)
         try:
             yield

@@ -37,6 +37,7 @@ CLASSES = [
     ("optimizer", re.compile(r"muon|adamw|sumsq|axpby|newton", re.I)),
 ]
 Interval = Tuple[float, float]
+STAGE_RX = re.compile(r"layer\d+\.(stage\d_[fbw])|^(prolog_[fb]|epilog_f|weight chunk|criterion|pipeline send/recv)$")
 
 
 def classify(name: str, cat: str) -> str:
@@ -54,14 +55,35 @@ def load_events(path: Path) -> List[dict]:
         data = json.load(f)
     events = data["traceEvents"] if isinstance(data, dict) else data
     out = []
+    launches: Dict[int, Tuple[object, float]] = {}  # correlation id -> (thread, launch time)
+    stages: Dict[object, List[Tuple[float, float, str]]] = defaultdict(list)  # thread -> (start, end, stage)
     for e in events:
-        if e.get("ph") == "X" and e.get("cat") in GPU_CATS and e.get("dur") is not None:
-            out.append({"name": e.get("name", "?"), "cat": e["cat"], "ts": float(e["ts"]), "dur": float(e["dur"]),
-                        "stream": (e.get("args") or {}).get("stream", e.get("tid", 0))})
+        if e.get("ph") != "X" or e.get("dur") is None:
+            continue
+        cat, args = e.get("cat"), (e.get("args") or {})
+        if cat in GPU_CATS:
+            out.append({"name": e.get("name", "?"), "cat": cat, "ts": float(e["ts"]), "dur": float(e["dur"]),
+                        "stream": args.get("stream", e.get("tid", 0)), "corr": args.get("correlation")})
+        elif cat == "cuda_runtime" and "correlation" in args:
+            launches[args["correlation"]] = ((e.get("pid"), e.get("tid")), float(e["ts"]))
+        elif cat == "user_annotation":
+            m = STAGE_RX.search(e.get("name", ""))
+            if m:
+                stages[(e.get("pid"), e.get("tid"))].append((float(e["ts"]), float(e["ts"]) + float(e["dur"]), m.group(1) or m.group(2)))
+    if stages and launches:  # captured with --with-cpu: attribute every kernel to the stage range open at its launch
+        import bisect
+
+        starts = {}
+        for th in stages:
+            stages[th].sort()
+            starts[th] = [r[0] for r in stages[th]]
+        for ev in out:
+            th, t = launches.get(ev.get("corr"), (None, None))
+            if th in stages:
+                i = bisect.bisect_right(starts[th], t) - 1
+                if i >= 0 and stages[th][i][1] >= t:
+                    ev["stage"] = stages[th][i][2]
     return out
-
-
-STAGE_RX = re.compile(r"layer\d+\.(stage\d_[fbw])|^(prolog_[fb]|epilog_f|weight chunk|criterion|pipeline send/recv)$")
 
 
 def load_events_sqlite(path: Path) -> List[dict]:

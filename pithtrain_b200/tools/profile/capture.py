@@ -34,7 +34,8 @@ def main(argv=None) -> None:
     ap.add_argument("script")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--out", type=Path, default=Path("workspace/profiles/step"))
-    ap.add_argument("--with-cpu", action="store_true", help="also record CPU-side operator and launch events")
+    ap.add_argument("--with-cpu", action="store_true",
+                    help="also record CPU-side operator and launch events and the engine's stage ranges (per-stage table)")
     ap.add_argument("--synthetic", action="store_true", help="ignore the script's dataset and use the synthetic stream")
     a = ap.parse_args(argv)
 
@@ -59,6 +60,10 @@ def main(argv=None) -> None:
     for _ in range(a.warmup):
         train_step(cfg)
     torch.cuda.synchronize()
+    if a.with_cpu:
+        from ...dualpipe import execution
+
+        execution.RECORD_RANGES = True  # stage ranges become annotations the analysis can attribute kernels to
     acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if a.with_cpu else [])
     with profile(activities=acts) as prof:
         with torch.profiler.record_function("profiled_step"):

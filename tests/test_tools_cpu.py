@@ -309,3 +309,49 @@ def test_profile_analyzer_reads_nsight_systems_sqlite_exports(tmp_path, capsys):
     assert A.main([str(tmp_path)]) == 0
     out = capsys.readouterr().out
     assert "stage2_f" in out and "communication overlapped with compute: 100.0%" in out
+
+
+def test_profile_analyzer_attributes_kernels_to_stage_annotations(tmp_path):
+    """A trace captured with ``--with-cpu``: stage ranges are ``user_annotation`` events on the launching thread and
+    kernels are tied to their launch through the correlation id."""
+    import json
+
+    from pithtrain_b200.tools.profile import analyze as A
+
+    ev = [
+        {"ph": "X", "cat": "user_annotation", "name": "layer00.stage1_f", "pid": 1, "tid": 5, "ts": 100.0, "dur": 50.0},
+        {"ph": "X", "cat": "user_annotation", "name": "layer00.stage3_w", "pid": 1, "tid": 5, "ts": 160.0, "dur": 20.0},
+        {"ph": "X", "cat": "user_annotation", "name": "profiled_step", "pid": 1, "tid": 5, "ts": 90.0, "dur": 500.0},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "pid": 1, "tid": 5, "ts": 110.0, "dur": 3.0, "args": {"correlation": 71}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "pid": 1, "tid": 5, "ts": 165.0, "dur": 3.0, "args": {"correlation": 72}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "pid": 1, "tid": 5, "ts": 300.0, "dur": 3.0, "args": {"correlation": 73}},
+        {"ph": "X", "cat": "kernel", "name": "pt::rmsnorm_fwd_kernel<8>()", "pid": 0, "tid": 7, "ts": 400.0, "dur": 10.0, "args": {"stream": 7, "correlation": 71}},
+        {"ph": "X", "cat": "kernel", "name": "void pt::gemm_bf16_kernel<256, true, true, false, true>()", "pid": 0, "tid": 7, "ts": 420.0, "dur": 30.0,
+         "args": {"stream": 7, "correlation": 72}},
+        {"ph": "X", "cat": "kernel", "name": "pt::muon_momentum_kernel()", "pid": 0, "tid": 7, "ts": 460.0, "dur": 5.0, "args": {"stream": 7, "correlation": 73}},
+    ]
+    path = tmp_path / "trace_rank0.json"
+    path.write_text(json.dumps({"traceEvents": ev}))
+    r = A.analyze_events(A.load_events(path))
+    assert r["stages"]["stage1_f"]["sum_us"] == 10.0 and r["stages"]["stage3_w"]["sum_us"] == 30.0
+    assert set(r["stages"]) == {"stage1_f", "stage3_w"}  # the optimizer kernel was launched outside any stage range
+    assert any("stage3_w" in line for line in A.render("rank0", r))
+
+
+def test_stage_ranges_become_profiler_annotations_when_recording():
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from pithtrain_b200.dualpipe import execution
+
+    assert execution.RECORD_RANGES is False
+    execution.RECORD_RANGES = True
+    try:
+        with profile(activities=[ProfilerActivity.CPU]) as prof:
+            with execution.nvtx_range("layer05.stage3_f"):
+                torch.ones(4) + 1
+    finally:
+        execution.RECORD_RANGES = False
+    assert any(e.name == "layer05.stage3_f" for e in prof.events())
+    with execution.nvtx_range("layer05.stage3_f"):  # default path: no CUDA here, plain pass-through
+        pass
