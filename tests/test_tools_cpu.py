@@ -355,3 +355,28 @@ def test_stage_ranges_become_profiler_annotations_when_recording():
     assert any(e.name == "layer05.stage3_f" for e in prof.events())
     with execution.nvtx_range("layer05.stage3_f"):  # default path: no CUDA here, plain pass-through
         pass
+
+
+def test_ncu_table_from_a_raw_page_export(tmp_path, capsys):
+    from pithtrain_b200.tools.profile import ncu_table as T
+
+    header = ["ID", "Kernel Name", "gpu__time_duration.sum", "dram__bytes_read.sum", "dram__bytes_write.sum",
+              "gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed", "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active",
+              "sm__throughput.avg.pct_of_peak_sustained_elapsed", "launch__registers_per_thread", "launch__shared_mem_per_block_dynamic",
+              "launch__grid_size", "launch__block_size", "lts__t_sector_hit_rate.pct",
+              "smsp__average_warps_issue_stalled_long_scoreboard_per_issue_active.ratio",
+              "smsp__average_warps_issue_stalled_barrier_per_issue_active.ratio",
+              "smsp__average_warps_issue_stalled_selected_per_issue_active.ratio"]
+    units = ["", "", "us", "Mbyte", "Mbyte", "%", "%", "%", "register/thread", "Kbyte/block", "", "", "%", "", "", ""]
+    row = ["0", "pt::rmsnorm_fwd_kernel<8>(...)", "10.00", "32.0", "32.0", "71.5", "0", "40.1", "32", "0", "4,096", "256", "12.5", "6.3", "1.2", "1.0"]
+    path = tmp_path / "raw_rmsnorm.csv"
+    path.write_text("==PROF== some banner line\n" + "\n".join(",".join(f'"{c}"' for c in r) for r in (header, units, row)) + "\n")
+    (d,) = T.parse_raw_csv(path.read_text())
+    assert d["time"] == ("10.00", "us") and d["kernel"][0].startswith("pt::rmsnorm") and d["stalls"][0] == "long_scoreboard 6.3, barrier 1.2"
+    assert T.main(["--csv", str(path), "--bytes", str(64e6)]) == 0
+    out = capsys.readouterr().out
+    assert "| raw_rmsnorm | pt::rmsnorm_fwd_kernel<8>(...) | 10.00 us | 32.0 Mbyte / 32.0 Mbyte | 71.5 %" in out
+    assert "HBM" in out and "4,096 x 256" in out
+    # 64 MB in 10 us = 6400 GB/s
+    frac = float(out.strip().splitlines()[-1].split("|")[-2].split()[0])
+    assert 0.9 < frac < 1.05
