@@ -255,6 +255,7 @@ def main() -> int:
                 "routing": ("natural (seeded random-init gate)" if args.routing == "natural"
                             else "force-balanced round-robin replay (benchmark mode)"), "ep_transport": args.ep_backend,
                 "l2": "inputs larger than L2: every step streams >10 GB of parameters and activations, no explicit flush",
+                "switches": {k: v for k, v in sorted(os.environ.items()) if k.startswith("PITHTRAIN_")},
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
