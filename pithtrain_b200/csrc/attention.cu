@@ -326,7 +326,7 @@ namespace {
 int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Sk, int Hq, int Hkv,
                     long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal, void* stream_) {
   using namespace pt;
-  if (S % AT_BM != 0 || Sk % AT_BN != 0 || Hq % Hkv != 0 || B <= 0 || (causal && S != Sk)) return -2;
+  if (S <= 0 || Sk <= 0 || S % AT_BM != 0 || Sk % AT_BN != 0 || Hkv <= 0 || Hq % Hkv != 0 || B <= 0 || (causal && S != Sk)) return -2;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   CUtensorMap tmQ, tmK, tmV;
   const uint64_t rows = (uint64_t)B * S, kv_rows = (uint64_t)B * Sk;
