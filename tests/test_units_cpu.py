@@ -441,3 +441,29 @@ def test_gated_delta_rule_chunked_equals_the_recurrence(S, chunk):
     assert torch.allclose(o1, o2, atol=2e-4, rtol=1e-4), float((o1 - o2).abs().max())
     for a, b in zip(g1, g2):
         assert torch.allclose(a, b, atol=5e-4, rtol=1e-3), float((a - b).abs().max())
+
+
+def test_new_entry_points_validate_their_arguments_on_the_host():
+    """Shape errors are refused with -2 before any CUDA call; valid shapes get as far as the tensor-map encoder, which
+    has no driver here and reports -3 — neither path launches or crashes without a GPU."""
+    import ctypes
+
+    from pithtrain_b200 import _native
+
+    lib = ROOT / "pithtrain_b200" / "_lib" / "libpithb200.so"
+    if not lib.exists():
+        pytest.skip("native library not built")
+    if torch.cuda.is_available():
+        pytest.skip("host-only check")
+    L = ctypes.CDLL(str(lib))
+    for name in ("pt_attn_fwd_causal", "pt_attn_fwd_block", "pt_gemm2cta_nt"):
+        fn = getattr(L, name)
+        fn.argtypes = [_native._CT[a] for a in _native.SIGS[name]]
+        fn.restype = ctypes.c_int
+    N = None
+    assert L.pt_attn_fwd_causal(N, N, N, N, N, 1, 100, 4, 2, 512, 256, 256, 512, 0.1, N) == -2  # S not a multiple of 128
+    assert L.pt_attn_fwd_causal(N, N, N, N, N, 1, 256, 5, 2, 640, 256, 256, 640, 0.1, N) == -2  # heads not divisible
+    assert L.pt_attn_fwd_block(N, N, N, N, N, 1, 256, 0, 4, 2, 512, 256, 256, 512, 0.1, N) == -2  # no keys
+    assert L.pt_attn_fwd_block(N, N, N, N, N, 1, 256, 128, 4, 2, 512, 256, 256, 512, 0.1, N) == -3
+    assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 60, 60, 60, 256, N) == -2  # K not a multiple of 8
+    assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 64, 64, 64, 256, N) == -3
