@@ -82,6 +82,6 @@ def launch(world: int, fn: Callable, *args, backend: str = "gloo", timeout: floa
 
 def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
     """``1 - 2<x,y>/(|x|^2+|y|^2)``: 0 for identical tensors, insensitive to tiny elements."""
-    x, y = x.double(), y.double()
+    x, y = x.detach().double(), y.detach().double()
     d = (x * x + y * y).sum()
     return 0.0 if d == 0 else float(1 - 2 * (x * y).sum() / d)
