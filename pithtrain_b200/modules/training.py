@@ -137,10 +137,15 @@ class TrainingCfg(SlottedDefault):
     """dtype of the flat gradient accumulators (fp32 matches the reference's reduce dtype)."""
     muon_momentum_dtype: Literal["fp32", "bf16"] = "fp32"
     offload_optimizer_state: bool = False
+    """Keep Muon momentum in pinned host memory and stream it through the GPU during the step."""
     optimizer_device_state_gb: float = 0.0
     """With ``offload_optimizer_state``: GiB of Muon momentum that stay on the device anyway."""
-    """Keep Muon momentum in pinned host memory and stream it through the GPU during the step."""
     max_grad_norm: float = 1.0
+    expert_grad_scaling: Literal["global-mean", "reference"] = "global-mean"
+    """``global-mean``: every parameter sees the gradient of the same global token-mean loss, whatever the mesh.
+    ``reference``: expert gradients are averaged over dp x cp only, so they are ``ep`` times larger than in a run
+    without expert parallelism — what FSDP2's per-mesh averaging gives the reference
+    (pithtrain/modules/training.py:341-342); use it to reproduce the reference's loss curves at ``ep > 1``."""
     num_hidden_layers_override: Optional[int] = None
     """Truncate the model (tests and smoke runs only)."""
     pipeline_overlap: bool = True
@@ -252,10 +257,14 @@ def materialize_small_params(model: nn.Module) -> None:
                 p.fill_(getattr(p, "_init_fill", 0.0))
 
 
-def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dtype: torch.dtype = torch.float32):
+def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dtype: torch.dtype = torch.float32,
+               expert_grad_divisor: Optional[int] = None):
     """Place the parameters of both chunks into flat shard groups (experts over dp×cp, the rest over
-    dp×cp×ep). ``hsdp`` shards inside cp(×ep) and replicates over dp."""
+    dp×cp×ep). ``hsdp`` shards inside cp(×ep) and replicates over dp. ``expert_grad_divisor`` (default ``ep``)
+    divides the expert gradients on top of the shard-group average; 1 reproduces the reference's scaling."""
     d = distributed
+    if expert_grad_divisor is None:
+        expert_grad_divisor = d.ep_size
     mesh = d.device_mesh
     groups = []
     for i, m in enumerate(modules):
@@ -273,7 +282,7 @@ def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dty
         else:
             raise ValueError(f"Unknown sharding_strategy: {sharding_strategy!r}")
         groups.extend(build_shard_groups(m, grad_dtype=grad_dtype, prefix=f"module.{i}.", device=d.device,
-                                         expert_grad_divisor=d.ep_size, **kw))
+                                         expert_grad_divisor=expert_grad_divisor, **kw))
     training.shard_groups = tuple(groups)
     return modules
 
@@ -313,7 +322,8 @@ def setup_model(cfg: TrainingCfg, distributed_cfg: Any) -> None:
         torch.set_default_dtype(prev)
     modules = nn.Sequential(*modules)
     gdt = torch.float32 if cfg.grad_dtype == "fp32" else torch.bfloat16
-    apply_fsdp(modules, getattr(distributed_cfg, "sharding_strategy", "fsdp"), gdt)
+    apply_fsdp(modules, getattr(distributed_cfg, "sharding_strategy", "fsdp"), gdt,
+               expert_grad_divisor=1 if cfg.expert_grad_scaling == "reference" else None)
     for m in modules:
         materialize_small_params(m)
         init_weights(m, config.num_hidden_layers, cfg.init_std, cfg.depth_scaled_init, seed=cfg.seed,

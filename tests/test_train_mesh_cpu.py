@@ -64,3 +64,7 @@ def test_benchmark_mode_balances_the_experts(tmp_path):
     out = tmp_path / "bench_mode.json"
     launch(2, train_worker.run_benchmark_mode, str(out), timeout=300.0)
     assert len(json.load(open(out))) == 2
+
+
+def test_reference_expert_gradient_scaling_is_a_switch():
+    launch(2, train_worker.run_expert_grad_scaling, timeout=300.0)

@@ -309,3 +309,34 @@ def run_benchmark_mode(rank: int, world: int, out_path: str):
     if rank == 0:
         assert all(math.isfinite(m["loss"]) for m in rows)
         json.dump([m["load_balance_loss"] for m in rows], open(out_path, "w"))
+
+
+def run_expert_grad_scaling(rank: int, world: int):
+    """``expert_grad_scaling``: the default divides expert gradients by ``ep`` (mesh-invariant loss curves); ``reference``
+    keeps the extra factor ``ep`` the reference's per-mesh averaging produces, so the first step's gradient norm is
+    larger by exactly the expert share."""
+    from pithtrain_b200.contexts import training
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import make_adamw_optimizer, make_constant_scheduler, setup_training
+    from pithtrain_b200.tasks.pretrain_lm import PretrainLMCfg, train_step
+
+    norms = {}
+    for i, mode in enumerate(("global-mean", "reference")):
+        cfg = PretrainLMCfg()
+        cfg.distributed.expert_parallel_size = world
+        t = cfg.training
+        t.model = dict(TINY_CPU, hidden_size=64, head_dim=16, moe_intermediate_size=32, vocab_size=128)
+        t.sequence_length, t.micro_batch_size, t.global_batch_size = 16, 1, 2 * world
+        t.lr, t.max_steps, t.dataset, t.max_grad_norm = 0.0, 1, None, 1e9
+        t.optimizer, t.scheduler = make_adamw_optimizer, make_constant_scheduler
+        t.param_dtype, t.grad_dtype = "fp32", "fp32"
+        t.expert_grad_scaling = mode
+        if i == 0:
+            setup_logging(cfg)
+            setup_distributed(cfg, failfast=False)
+        setup_training(cfg)
+        divisors = sorted({g.grad_divisor for g in training.shard_groups})
+        assert divisors == ([1, world] if mode == "global-mean" else [1]), (mode, divisors)
+        norms[mode] = train_step(cfg)["gradient_norm"]
+    assert norms["reference"] > norms["global-mean"] * 1.0001, norms
