@@ -105,8 +105,8 @@ SIGS = {
     "pt_quant_rows": "PLPIPIIPPLP",
     "pt_quant_blocks": "PIIIPPPPP",
     "pt_gemm_fp8": "PPPIIIILLLLPLPPIIIIP",
-    "pt_attn_fwd_causal": "PPPPPIIIILLLLFP",
-    "pt_attn_fwd_block": "PPPPPIIIIILLLLFP",
+    "pt_attn_fwd": "PPPPPPP" + "IIIIIII" + "LLLL" + "F" + "II" + "P",
+    "pt_attn_bwd": "PPPPPPPPPPPPPPP" + "IIIIII" + "LLLLL" + "F" + "II" + "P",
     "pt_gemm2cta_nt": "PPPIIILLLP",
 }
 
@@ -131,7 +131,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 # Number of kernel launches issued through this module since it was last reset (bench bookkeeping).
 LAUNCHES = 0
-_LAUNCHES_PER_CALL = {"pt_route_sort": 4}
+_LAUNCHES_PER_CALL = {"pt_route_sort": 4, "pt_attn_bwd": 5}
 
 
 def check(rc: int, what: str) -> None:

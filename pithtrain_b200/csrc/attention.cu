@@ -1,90 +1,113 @@
-// GQA attention forward for sm_100a, head dim 128, bf16 (tcgen05 / TMEM / TMA): causal self-attention, and the
-// unmasked block form that ring attention uses (K/V may then live in another GPU's published buffer).
+// Attention forward for sm_100a (tcgen05 / TMEM / TMA), bf16 in, fp32 accumulate: causal or unmasked, GQA, per-row
+// lower key bounds (sliding windows and packed documents), learned per-head sinks, head dims 64, 128, 192/128 (MLA)
+// and 256. Takes the role of the reference's FlashAttention-4 forward (pithtrain/operators/flash_attn_v4.py:17-45,
+// :58-70). K and V may point into another GPU's published buffer (plain, non-multicast TMA loads), which is how the
+// context-parallel ring reads a peer's block while computing on it.
 //
-// Status: compiles for sm_100a (63 registers, no spills) but has not been validated on hardware yet, so nothing
-// calls it unless PITHTRAIN_OWN_ATTENTION=1 is set (see ops/attention_native.py); the default attention path is the
-// library kernel. The role of the reference's FlashAttention-4 forward (pithtrain/operators/flash_attn_v4.py:17-45).
+//   grid  = (ceil(q tiles / NQ), Hq, B); a CTA owns NQ (two, where TMEM allows) consecutive 128-row query tiles of one
+//           head and walks the key tiles they can see; CTAs with the most key tiles are scheduled first.
+//   warp 0          TMA producer : Q tiles once, then K and V tiles of 128 keys through KST-stage rings
+//   warp 1          MMA issuer   : S_t = Q_t K^T into TMEM; O_t += P_t V with P_t read from TMEM
+//   warps 2..5      softmax of tile 0, warps 6..9 softmax of tile 1: one thread per query row (tcgen05.ld 32x32b hands
+//                   thread t row t of the warp's lane quarter, so row max / row sum need no shuffles). The row's 128
+//                   scores are held in registers; P is written back over S in TMEM as packed bf16 (64 columns) and
+//                   feeds the P V MMA from there, so P never touches shared memory. O is rescaled lazily (only when a
+//                   row maximum grows by more than 2^8). The two tiles alternate on the tensor core: while one tile's
+//                   softmax runs, the other tile's P V and next S are in flight.
 //
-//   grid  = (S / 128 query tiles, Hq, B), longest (last) query tile first
-//   warp 0      TMA producer : Q tile once, then K and V tiles of 128 keys through two-stage rings
-//   warp 1      MMA issuer   : S = Q K^T into one of two TMEM buffers, O += P V into a third
-//   warps 2..5  softmax      : one thread per query row (tcgen05.ld 32x32b hands thread t row t of the
-//                              warp's lane quarter, so row max / row sum need no shuffles); writes P as
-//                              bf16 into a 128B-swizzled K-major shared-memory tile for the PV MMA;
-//                              rescales O lazily (only when a row maximum grows by more than 2^8)
-//
-// Layouts: q [B*S, Hq*128], k/v [B*S, Hkv*128] (token-major, as the qkv projection writes them),
-// out [B*S, Hq*128] bf16, lse [B, Hq, S] fp32 (natural log of the scaled scores' sum).
-// TMEM: 512 columns = S0 | S1 | O | unused.  Shared memory: Q 32 KB, K 2x32 KB, V 2x32 KB, P 32 KB.
-//
-// Every wait is bounded (mbar_wait_bounded); on a timeout the roles leave their loops, the CTA frees
-// its TMEM and the status word carries the code.
+// Visibility of key kp for the query at row r (absolute position qpos = q_off + r):
+//   lo[r] <= kp <= (causal ? qpos : Sk - 1), with lo[r] = row_lo ? row_lo[b * Sq + r] : 0 (non-decreasing in r).
+// Layouts: q [B*Sq, Hq*DQK], k [B*Sk, Hkv*DQK], v [B*Sk, Hkv*DV] (token-major with row pitches), out [B*Sq, Hq*DV]
+// bf16, lse [B, Hq, Sq] fp32 (natural log; includes the sink when one is given).
+// TMEM: S_0 | S_1 | O_0 | O_1.  Every wait is bounded (mbar_wait_bounded); on a timeout the roles leave their loops,
+// the CTA frees its TMEM and the status word carries the code.
 #include "host_common.h"
 #include "ptx.cuh"
 
 namespace pt {
 
-constexpr int AT_BM = 128;       // query rows per CTA
-constexpr int AT_BN = 128;       // keys per KV tile
-constexpr int AT_D = 128;        // head dim
-constexpr int AT_KSTAGES = 2;
-constexpr int AT_TILE = 128 * 64 * 2;           // one [128 x 64] bf16 swizzle slab: 16 KB
-constexpr int AT_Q_BYTES = 2 * AT_TILE;         // D = 128 = two slabs
-constexpr int AT_K_BYTES = 2 * AT_TILE;
-constexpr int AT_V_BYTES = 2 * AT_TILE;         // two 64-key blocks x (two [64 x 64] boxes)
-constexpr int AT_P_BYTES = 2 * AT_TILE;
-constexpr float AT_RESCALE_LOG2 = 8.0f;         // tolerated growth of a row maximum before O is rescaled
+constexpr int AT_SLAB = 128 * 64 * 2;      // one [128 x 64] bf16 swizzle slab: 16 KB
+constexpr float AT_RESCALE_LOG2 = 8.0f;    // tolerated growth of a row maximum before O is rescaled
 
 struct AttnArgs {
-  int B, S, Sk, Hq, Hkv;  // S query tokens and Sk key tokens per batch entry
-  int causal;            // 1: self-attention with the causal mask (S == Sk); 0: every query sees every key (ring blocks)
-  float scale_log2;  // softmax scale * log2(e)
+  int B, Sq, Sk, Hq, Hkv;
+  int causal;         // 1: key position <= query position
+  int q_off;          // absolute position of query row 0 relative to key 0
+  float scale_log2;   // softmax scale * log2(e)
+  const int* row_lo;  // optional per-row lower key bound [B*Sq]
+  const float* sinks; // optional per-head sink logits [Hq]
   __nv_bfloat16* out;
-  long long ldo;     // elements between consecutive tokens of out
+  long long ldo;      // elements between consecutive tokens of out
   float* lse;
   int* err;
 };
 
-__global__ void __launch_bounds__(192, 1)
+template <int DQK, int DV, int NQ, int KST>
+struct AttnFwdCfg {
+  static constexpr int Q_BYTES = (DQK / 64) * AT_SLAB;
+  static constexpr int K_BYTES = Q_BYTES;
+  static constexpr int V_BYTES = (DV / 64) * AT_SLAB;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM = NQ * Q_BYTES + KST * (K_BYTES + V_BYTES) + BAR_BYTES + 1024;
+  static constexpr int THREADS = 64 + 128 * NQ;
+  static_assert(NQ * 128 + NQ * DV <= 512, "TMEM columns");
+};
+
+template <int DQK, int DV, int NQ, int KST>
+__global__ void __launch_bounds__(64 + 128 * NQ, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnArgs args) {
+  using Cfg = AttnFwdCfg<DQK, DV, NQ, KST>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + AT_Q_BYTES;
-  uint8_t* sV = sK + AT_KSTAGES * AT_K_BYTES;
-  uint8_t* sP = sV + AT_KSTAGES * AT_V_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + AT_P_BYTES);
-  uint64_t* q_full = bars;                  // 1
-  uint64_t* k_full = bars + 1;              // 2
-  uint64_t* k_empty = bars + 3;             // 2
-  uint64_t* v_full = bars + 5;              // 2
-  uint64_t* v_empty = bars + 7;             // 2
-  uint64_t* s_full = bars + 9;              // 2  MMA -> softmax
-  uint64_t* s_empty = bars + 11;            // 2  softmax (4 warps) -> MMA
-  uint64_t* p_full = bars + 13;             // 1  softmax (128 threads) -> MMA
-  uint64_t* pv_done = bars + 14;            // 1  MMA -> softmax: PV of a tile finished (P free, O readable)
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  uint8_t* sK = sQ + NQ * Cfg::Q_BYTES;
+  uint8_t* sV = sK + KST * Cfg::K_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KST * Cfg::V_BYTES);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* k_full = bars + 1;             // KST (<= 4)
+  uint64_t* k_empty = bars + 5;            // KST
+  uint64_t* v_full = bars + 9;             // KST
+  uint64_t* v_empty = bars + 13;           // KST
+  uint64_t* s_full = bars + 17;            // NQ  MMA -> softmax
+  uint64_t* p_full = bars + 19;            // NQ  softmax (4 warps) -> MMA
+  uint64_t* o_done = bars + 21;            // NQ  MMA -> softmax: last P V of the tile finished
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 23);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy tiles first
+  const int pair = gridDim.x - 1 - blockIdx.x;  // heavy CTAs first (causal: the last query tiles see the most keys)
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (args.Hq / args.Hkv);
-  const int q0 = qt * AT_BM;
-  const int n_kv = args.causal ? qt + 1 : args.Sk / AT_BN;  // causal: key tiles 0..qt
-  const int row_base = b * args.S;
+  const int nK = (args.Sk + 127) / 128;
+  const int row_base = b * args.Sq;
   const int kv_base = b * args.Sk;
+
+  // key-tile range [lo_t, hi_t) of each query tile; J0..J1 is their union
+  int lo_t[NQ], hi_t[NQ];
+  int J0 = 1 << 30, J1 = 0;
+#pragma unroll
+  for (int t = 0; t < NQ; ++t) {
+    const int q0 = (pair * NQ + t) * 128;
+    lo_t[t] = hi_t[t] = 0;
+    if (q0 < args.Sq) {
+      const int last = min(q0 + 127, args.Sq - 1);
+      int lo = args.row_lo ? args.row_lo[row_base + q0] : 0;
+      int hi = args.causal ? min(args.Sk - 1, args.q_off + last) : args.Sk - 1;  // last visible key of the tile
+      lo = max(lo, 0);
+      if (hi >= lo) { lo_t[t] = lo / 128; hi_t[t] = min(nK, hi / 128 + 1); }
+      if (hi_t[t] > lo_t[t]) { J0 = min(J0, lo_t[t]); J1 = max(J1, hi_t[t]); }
+    }
+  }
+  if (J1 == 0) J0 = 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < AT_KSTAGES; ++s) {
+    for (int s = 0; s < KST; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
+    for (int t = 0; t < NQ; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -97,47 +120,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
-  const uint32_t tS0 = tmem_base, tO = tmem_base + 256;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    if (lane == 0) {
-      mbar_expect_tx(q_full, AT_Q_BYTES);
-      tma_load_2d(sQ, &tmQ, q_full, h * AT_D, row_base + q0);
-      tma_load_2d(sQ + AT_TILE, &tmQ, q_full, h * AT_D + 64, row_base + q0);
-      int issued_k = 0, issued_v = 0;
+    if (lane == 0 && J1 > J0) {
+      int nq_act = 0;
+#pragma unroll
+      for (int t = 0; t < NQ; ++t) nq_act += (hi_t[t] > lo_t[t]) ? 1 : 0;
+      mbar_expect_tx(q_full, nq_act * Cfg::Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < NQ; ++t)
+        if (hi_t[t] > lo_t[t])
+#pragma unroll
+          for (int db = 0; db < DQK / 64; ++db)
+            tma_load_2d(sQ + t * Cfg::Q_BYTES + db * AT_SLAB, &tmQ, q_full, h * DQK + 64 * db, row_base + (pair * NQ + t) * 128);
+      int issued = 0;
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j % AT_KSTAGES;
-        const uint32_t ph = (j / AT_KSTAGES) & 1;
-        const int kv0 = kv_base + j * AT_BN;
+      for (int j = J0; j < J1 && ok; ++j, ++issued) {
+        const int s = issued % KST;
+        const uint32_t ph = (issued / KST) & 1;
+        const int kv0 = kv_base + j * 128;
         ok = mbar_wait_bounded(&k_empty[s], ph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
         if (!ok) break;
-        mbar_expect_tx(&k_full[s], AT_K_BYTES);
-        tma_load_2d(sK + s * AT_K_BYTES, &tmK, &k_full[s], hk * AT_D, kv0);
-        tma_load_2d(sK + s * AT_K_BYTES + AT_TILE, &tmK, &k_full[s], hk * AT_D + 64, kv0);
-        ++issued_k;
+        mbar_expect_tx(&k_full[s], Cfg::K_BYTES);
+#pragma unroll
+        for (int db = 0; db < DQK / 64; ++db)
+          tma_load_2d(sK + s * Cfg::K_BYTES + db * AT_SLAB, &tmK, &k_full[s], hk * DQK + 64 * db, kv0);
         ok = mbar_wait_bounded(&v_empty[s], ph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
         if (!ok) break;
-        mbar_expect_tx(&v_full[s], AT_V_BYTES);
-        // MN-major B operand: per 64-key block, two [64 keys x 64 d] boxes 8 KB apart
+        mbar_expect_tx(&v_full[s], Cfg::V_BYTES);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int db = 0; db < 2; ++db)
-            tma_load_2d(sV + s * AT_V_BYTES + kb * AT_TILE + db * 8192, &tmV, &v_full[s], hk * AT_D + 64 * db, kv0 + 64 * kb);
-        ++issued_v;
+        for (int db = 0; db < DV / 64; ++db)
+          tma_load_2d(sV + s * Cfg::V_BYTES + db * AT_SLAB, &tmV, &v_full[s], hk * DV + 64 * db, kv0);
       }
       if (*abort_flag) {
-        // let copies in flight land before the CTA retires
-        uint64_t t0 = globaltimer_ns();
+        // let copies in flight land before the CTA retires (bounded)
+        const uint64_t t0 = globaltimer_ns();
         bool drained = false;
         while (!drained && globaltimer_ns() - t0 < 20000000ull) {
           drained = mbar_try_wait(q_full, 0);
-          for (int i = 0; i < AT_KSTAGES && drained; ++i) {
-            const int jk = issued_k - 1 - i, jv = issued_v - 1 - i;
-            if (jk >= 0) drained = drained && mbar_try_wait(&k_full[jk % AT_KSTAGES], (jk / AT_KSTAGES) & 1);
-            if (jv >= 0) drained = drained && mbar_try_wait(&v_full[jv % AT_KSTAGES], (jv / AT_KSTAGES) & 1);
+          for (int i = 0; i < KST && drained; ++i) {
+            const int c = issued - 1 - i;
+            if (c >= 0) {
+              drained = drained && mbar_try_wait(&k_full[c % KST], (c / KST) & 1);
+              drained = drained && mbar_try_wait(&v_full[c % KST], (c / KST) & 1);
+            }
           }
         }
         if (!drained && args.err) atomicCAS(args.err, 0, PT_ERR_TIMEOUT_DRAIN);
@@ -145,169 +172,180 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc(1, 1, AT_BM, AT_BN, false, false);
-      constexpr uint32_t IDESC_O = make_idesc(1, 1, AT_BM, AT_D, false, true);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+    if (lane == 0 && J1 > J0) {
+      constexpr uint32_t IDESC_S = make_idesc(1, 1, 128, 128, false, false);
+      constexpr uint32_t IDESC_O = make_idesc(1, 1, 128, DV, false, true);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-      auto issue_S = [&](int j) -> bool {
-        const int s = j % AT_KSTAGES, sb = j & 1;
-        if (!mbar_wait_bounded(&s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA)) return false;
-        if (!mbar_wait_bounded(&k_full[s], (j / AT_KSTAGES) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA)) return false;
+      int kwaited = J0 - 1, vwaited = J0 - 1;  // last key tile whose K / V arrival has been observed
+      auto act = [&](int t, int j) { return j >= lo_t[t] && j < hi_t[t]; };
+      auto issue_S = [&](int t, int j) -> bool {
+        const int c = j - J0, s = c % KST;
+        if (kwaited < j) {
+          if (!mbar_wait_bounded(&k_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA)) return false;
+          kwaited = j;
+        }
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + s * AT_K_BYTES);
+        const uint32_t q_addr = smem_u32(sQ + t * Cfg::Q_BYTES), k_addr = smem_u32(sK + s * Cfg::K_BYTES);
 #pragma unroll
-        for (int db = 0; db < 2; ++db)
+        for (int db = 0; db < DQK / 64; ++db)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16(tS0 + sb * AT_BN, make_smem_desc_sw128(q_addr + db * AT_TILE + k * 32, 16, 1024),
-                     make_smem_desc_sw128(k_addr + db * AT_TILE + k * 32, 16, 1024), IDESC_S, (db | k) != 0 ? 1u : 0u);
-        umma_commit(&k_empty[s]);
-        umma_commit(&s_full[sb]);
+            umma_f16(tmem_base + t * 128, make_smem_desc_sw128(q_addr + db * AT_SLAB + k * 32, 16, 1024),
+                     make_smem_desc_sw128(k_addr + db * AT_SLAB + k * 32, 16, 1024), IDESC_S, (db | k) != 0 ? 1u : 0u);
+        umma_commit(&s_full[t]);
         return true;
       };
-      if (ok) ok = issue_S(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) { ok = issue_S(j + 1); if (!ok) break; }
-        const int s = j % AT_KSTAGES;
-        ok = mbar_wait_bounded(p_full, j & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        ok = mbar_wait_bounded(&v_full[s], (j / AT_KSTAGES) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + s * AT_V_BYTES);
+      if (ok) {
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
+        for (int t = 0; t < NQ; ++t)
+          if (ok && act(t, J0)) ok = issue_S(t, J0);
+        if (ok) umma_commit(&k_empty[0]);
+      }
+      for (int j = J0; j < J1 && ok; ++j) {
+        const int c = j - J0, s = c % KST;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tO, make_smem_desc_sw128(p_addr + kb * AT_TILE + k * 32, 16, 1024),
-                     make_smem_desc_sw128(v_addr + kb * AT_TILE + k * 2048, 8192, 1024), IDESC_O,
-                     (j | kb | k) != 0 ? 1u : 0u);
+        for (int t = 0; t < NQ; ++t) {
+          if (!ok) break;
+          if (act(t, j)) {
+            ok = mbar_wait_bounded(&p_full[t], (j - lo_t[t]) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+            if (vwaited < j) {
+              ok = mbar_wait_bounded(&v_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+              if (!ok) break;
+              vwaited = j;
+            }
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(sV + s * Cfg::V_BYTES);
+            const uint32_t tP = tmem_base + t * 128, tO = tmem_base + NQ * 128 + t * DV;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              umma_f16_ts(tO, tP + k * 8, make_smem_desc_sw128(v_addr + k * 2048, AT_SLAB, 1024), IDESC_O,
+                          (j != lo_t[t] || k != 0) ? 1u : 0u);
+            if (j == hi_t[t] - 1) umma_commit(&o_done[t]);
+          }
+          if (j + 1 < J1 && act(t, j + 1)) ok = issue_S(t, j + 1);
+        }
+        if (!ok) break;
         umma_commit(&v_empty[s]);
-        umma_commit(pv_done);
+        if (j + 1 < J1) umma_commit(&k_empty[(c + 1) % KST]);
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax (one thread per row)
-    const int q = warp & 3;
+    const int t = (warp - 2) >> 2;            // query tile of this warp group
+    const int q = warp & 3;                   // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;              // row of the tile
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    const int qpos = q0 + r;
+    const int qrow = (pair * NQ + t) * 128 + r;        // row within the batch entry
+    const bool row_valid = qrow < args.Sq;
+    const int jlo = lo_t[t], jhi = hi_t[t];
+    int lo_row = 0, hi_row = -1;
+    if (row_valid) {
+      lo_row = args.row_lo ? max(args.row_lo[row_base + qrow], 0) : 0;
+      hi_row = args.causal ? min(args.Sk - 1, args.q_off + qrow) : args.Sk - 1;
+    }
+    const uint32_t tS = tmem_base + lane_off + t * 128;
+    const uint32_t tO = tmem_base + lane_off + NQ * 128 + t * DV;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int sb = j & 1;
+    for (int j = jlo; j < jhi; ++j) {
       int good = 1;
-      if (lane == 0) good = mbar_wait_bounded(&s_full[sb], (j >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+      if (lane == 0) good = mbar_wait_bounded(&s_full[t], (j - jlo) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { ok = false; break; }
       tc_fence_after();
-      const uint32_t tS = tS0 + lane_off + sb * AT_BN;
-      const bool diag = args.causal && (j == qt);
-      const int kpos0 = j * AT_BN;
-      // pass 1: row maximum (log2 domain)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
+      uint32_t sv[128];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (diag && kpos0 + c * 32 + i > qpos) x = -INFINITY;
-          mx = fmaxf(mx, x);
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
+      tmem_ld_wait();
+      const int kpos0 = j * 128;
+      if (kpos0 < lo_row || kpos0 + 127 > hi_row) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (kpos0 + i < lo_row || kpos0 + i > hi_row) sv[i] = 0xff800000u;  // -inf
       }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
       const float m_new = fmaxf(m_ref, mx * args.scale_log2);  // scale > 0
-      // the previous PV must be done before P is overwritten and before O may be rescaled
-      if (j > 0) {
-        if (lane == 0) good = mbar_wait_bounded(pv_done, (j - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) { ok = false; break; }
-        tc_fence_after();
-      }
+      // The S MMA of this step was issued after the P V MMA of the previous one, so O is stable here.
       const bool grow = m_new > m_ref + AT_RESCALE_LOG2;
-      if (j == 0) {
+      if (j == jlo) {
         m_ref = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         // warp-uniform branch: tcgen05.ld/st are warp-collective
-        const float alpha = exp2f(m_ref - m_new);
+        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);
         m_ref = m_new;
         l *= alpha;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < DV / 32; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32(tO + lane_off + c * 32, v);
+          tmem_ld_32x32(tO + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tO + lane_off + c * 32, v);
+          tmem_st_32x32(tO + c * 32, v);
         }
-        tmem_st_wait();
       }
-      // pass 2: p = 2^(s - m_ref), row sum, bf16 P tile (K-major, 128-byte swizzle)
-      uint8_t* prow = sP + r * 128;
-#pragma unroll 1
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        if (c == 3) {
-          // S has left TMEM: hand the buffer back for tile j + 2
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s_empty[sb]);
-        }
-        float p[32];
+        // chunk c holds keys [32c, 32c+32) -> packed bf16 columns [16c, 16c+16) of the same TMEM region
+        uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = fmaf(__uint_as_float(v[i]), args.scale_log2, -m_ref);
-          float e = exp2f(x);
-          if (diag && kpos0 + c * 32 + i > qpos) e = 0.f;
-          p[i] = e;
-          l += e;
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = exp2f(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), args.scale_log2, -m_use));
+          const float e1 = exp2f(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), args.scale_log2, -m_use));
+          l += e0 + e1;
+          w[i] = pack_bf16x2(e0, e1);
         }
-        uint8_t* blk = prow + (c >> 1) * AT_TILE;  // 64-key block
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint4 w;
-          w.x = pack_bf16x2(p[8 * t + 0], p[8 * t + 1]);
-          w.y = pack_bf16x2(p[8 * t + 2], p[8 * t + 3]);
-          w.z = pack_bf16x2(p[8 * t + 4], p[8 * t + 5]);
-          w.w = pack_bf16x2(p[8 * t + 6], p[8 * t + 7]);
-          const int chunk = (c & 1) * 4 + t;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ (r & 7)) << 4)) = w;
-        }
+        tmem_st_32x16(tS + c * 16, w);
       }
-      tc_fence_before();          // orders the tcgen05.st of a rescale before the MMA thread's PV
-      fence_proxy_async_smem();   // generic-proxy writes of P before the async-proxy reads of the MMA
-      mbar_arrive(p_full);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
     }
     if (ok) {
       int good = 1;
-      if (lane == 0) good = mbar_wait_bounded(pv_done, (n_kv - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
-      good = __shfl_sync(0xffffffffu, good, 0);
-      if (good) {
+      if (jhi > jlo) {
+        if (lane == 0) good = mbar_wait_bounded(&o_done[t], 0, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+      }
+      if (good && (pair * NQ + t) * 128 < args.Sq) {
         tc_fence_after();
-        const float inv = 1.f / l;
-        __nv_bfloat16* orow = args.out + (long long)(row_base + qpos) * args.ldo + h * AT_D;
+        float lt = l, mr = m_ref;
+        if (args.sinks) {
+          const float s2 = args.sinks[h] * 1.4426950408889634f;
+          if (mr == -INFINITY) { mr = s2; lt = 1.f; }
+          else lt += exp2f(s2 - mr);
+        }
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        __nv_bfloat16* orow = args.out + (long long)(row_base + qrow) * args.ldo + h * DV;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < DV / 32; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32(tO + lane_off + c * 32, v);
-          tmem_ld_wait();
+          if (jhi > jlo) {
+            tmem_ld_32x32(tO + c * 32, v);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * t + 0]) * inv, __uint_as_float(v[8 * t + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(v[8 * t + 2]) * inv, __uint_as_float(v[8 * t + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(v[8 * t + 4]) * inv, __uint_as_float(v[8 * t + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(v[8 * t + 6]) * inv, __uint_as_float(v[8 * t + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + t * 8) = w;
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+            }
           }
         }
-        args.lse[((long long)b * args.Hq + h) * args.S + qpos] = m_ref * 0.6931471805599453f + logf(l);
+        if (row_valid)
+          args.lse[((long long)b * args.Hq + h) * args.Sq + qrow] = lt > 0.f ? mr * 0.6931471805599453f + logf(lt) : -INFINITY;
       }
     }
   }
@@ -323,45 +361,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }  // namespace pt
 
 namespace {
-int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Sk, int Hq, int Hkv,
-                    long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal, void* stream_) {
-  using namespace pt;
-  if (S <= 0 || Sk <= 0 || S % AT_BM != 0 || Sk % AT_BN != 0 || Hkv <= 0 || Hq % Hkv != 0 || B <= 0 || (causal && S != Sk)) return -2;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+using namespace pt;
+
+template <int DQK, int DV, int NQ, int KST>
+int attn_fwd_launch_t(const void* q, const void* k, const void* v, const AttnArgs& a, long long ldq, long long ldk,
+                      long long ldv, cudaStream_t stream) {
+  using Cfg = AttnFwdCfg<DQK, DV, NQ, KST>;
   CUtensorMap tmQ, tmK, tmV;
-  const uint64_t rows = (uint64_t)B * S, kv_rows = (uint64_t)B * Sk;
-  if (encode_tmap_2d(&tmQ, q, TM_BF16, rows, (uint64_t)Hq * AT_D, ldq, 128, 64, TM_SW_128)) return -3;
-  if (encode_tmap_2d(&tmK, k, TM_BF16, kv_rows, (uint64_t)Hkv * AT_D, ldk, 128, 64, TM_SW_128)) return -3;
-  if (encode_tmap_2d(&tmV, v, TM_BF16, kv_rows, (uint64_t)Hkv * AT_D, ldv, 64, 64, TM_SW_128)) return -3;
-  AttnArgs a;
-  a.B = B; a.S = S; a.Sk = Sk; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
-  a.scale_log2 = scale * 1.4426950408889634f;
-  a.out = static_cast<__nv_bfloat16*>(out); a.ldo = ldo;
-  a.lse = static_cast<float*>(lse);
-  a.err = device_status_word();
-  const int smem = AT_Q_BYTES + AT_KSTAGES * (AT_K_BYTES + AT_V_BYTES) + AT_P_BYTES + 256 + 1024;
+  const uint64_t rows = (uint64_t)a.B * a.Sq, kv_rows = (uint64_t)a.B * a.Sk;
+  if (encode_tmap_2d(&tmQ, q, TM_BF16, rows, (uint64_t)a.Hq * DQK, ldq, 128, 64, TM_SW_128)) return -3;
+  if (encode_tmap_2d(&tmK, k, TM_BF16, kv_rows, (uint64_t)a.Hkv * DQK, ldk, 128, 64, TM_SW_128)) return -3;
+  if (encode_tmap_2d(&tmV, v, TM_BF16, kv_rows, (uint64_t)a.Hkv * DV, ldv, 128, 64, TM_SW_128)) return -3;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<DQK, DV, NQ, KST>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+        cudaSuccess)
+      return -4;
     configured = true;
   }
-  dim3 grid(S / AT_BM, Hq, B);
-  attn_fwd_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, a);
+  const int nQ = (a.Sq + 127) / 128;
+  dim3 grid((nQ + NQ - 1) / NQ, a.Hq, a.B);
+  attn_fwd_kernel<DQK, DV, NQ, KST><<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 }  // namespace
 
-// q [B*S, Hq*128], k, v [B*S, Hkv*128] bf16 with row pitches ldq / ldk / ldv (elements); S a multiple of 128.
-PT_API int pt_attn_fwd_causal(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Hq, int Hkv,
-                              long long ldq, long long ldk, long long ldv, long long ldo, float scale, void* stream_) {
-  return attn_fwd_launch(q, k, v, out, lse, B, S, S, Hq, Hkv, ldq, ldk, ldv, ldo, scale, 1, stream_);
-}
-
-// Block form for ring attention: S query tokens against Sk key tokens per batch entry, no mask. k and v may point
-// into another GPU's published buffer (plain, non-multicast TMA loads read it over NVLink), so the block can be
-// computed while it is being fetched instead of after a copy.
-PT_API int pt_attn_fwd_block(const void* q, const void* k, const void* v, void* out, void* lse, int B, int S, int Sk, int Hq,
-                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
-                             void* stream_) {
-  return attn_fwd_launch(q, k, v, out, lse, B, S, Sk, Hq, Hkv, ldq, ldk, ldv, ldo, scale, 0, stream_);
+// q [B*Sq, Hq*dqk], k [B*Sk, Hkv*dqk], v [B*Sk, Hkv*dv] bf16 with row pitches ldq / ldk / ldv (elements, multiples of
+// 8, 16-byte aligned bases). (dqk, dv) in {(64,64), (128,128), (192,128), (256,256)}. row_lo (int32 [B*Sq]) and sinks
+// (fp32 [Hq]) may be null. Returns 0, or a negative code for unsupported arguments / launch failures.
+PT_API int pt_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse, const void* row_lo, const void* sinks,
+                       int B, int Sq, int Sk, int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv,
+                       long long ldo, float scale, int causal, int q_off, void* stream_) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || Hkv <= 0 || Hq % Hkv != 0 || scale <= 0.f) return -2;
+  AttnArgs a;
+  a.B = B; a.Sq = Sq; a.Sk = Sk; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.q_off = q_off;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.row_lo = static_cast<const int*>(row_lo);
+  a.sinks = static_cast<const float*>(sinks);
+  a.out = static_cast<__nv_bfloat16*>(out); a.ldo = ldo;
+  a.lse = static_cast<float*>(lse);
+  a.err = device_status_word();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (dqk == 128 && dv == 128) return attn_fwd_launch_t<128, 128, 2, 2>(q, k, v, a, ldq, ldk, ldv, stream);
+  if (dqk == 64 && dv == 64) return attn_fwd_launch_t<64, 64, 2, 3>(q, k, v, a, ldq, ldk, ldv, stream);
+  if (dqk == 192 && dv == 128) return attn_fwd_launch_t<192, 128, 1, 2>(q, k, v, a, ldq, ldk, ldv, stream);
+  if (dqk == 256 && dv == 256) return attn_fwd_launch_t<256, 256, 1, 1>(q, k, v, a, ldq, ldk, ldv, stream);
+  return -2;
 }

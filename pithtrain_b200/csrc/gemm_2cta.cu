@@ -1,7 +1,7 @@
 // Dense bf16 NT GEMM with 2-CTA tcgen05 tiles (cta_group::2).
 //
-// Status: compiles for sm_100a (93 registers, no spills) but has not been validated on hardware yet; nothing calls it
-// unless PITHTRAIN_GEMM_2CTA=1 is set (ops/gemm.py). The single-CTA family in gemm.cu is the default everywhere.
+// Default path of ops/gemm.py: gemm_nt for fresh bf16 outputs (q/k/v/o projections, lm_head, dense MLPs); the
+// single-CTA family in gemm.cu serves the accumulating, fp32-output, NN / TN and grouped forms.
 //
 //   D[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate in TMEM, bf16 out through TMA stores.
 //   A pair of CTAs (cluster 2x1x1) owns a 256 x 256 output tile: CTA r loads rows [m0 + 128 r, +128) of A and rows

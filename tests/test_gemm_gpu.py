@@ -166,8 +166,6 @@ def test_grouped_gather_matches_explicit_gather(sizes, N, K):
     assert torch.equal(out2[:last], ref2[:last])
 
 
-@pytest.mark.skipif(os.environ.get("PITHTRAIN_GEMM_2CTA", "0") != "1",
-                    reason="the cta_group::2 GEMM runs only with PITHTRAIN_GEMM_2CTA=1 until it is validated")
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (4096, 5120, 2048), (300, 200, 136)])
 def test_two_cta_gemm_nt(M, N, K):
     from pithtrain_b200.ops import gemm as G
