@@ -33,6 +33,7 @@ STATUS_NAMES = {
     4: "timeout waiting for a peer",
     5: "receive-buffer capacity exceeded",
     6: "timeout draining in-flight copies",
+    7: "dynamic shared memory not 1024-byte aligned",
 }
 
 
@@ -54,6 +55,7 @@ def lib() -> ctypes.CDLL:
 SIGS = {
     "pt_status_fetch_and_clear": "",
     "pt_sm_count": "",
+    "pt_set_peer_wait_limit_ns": "L",
     "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIPILP",
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
@@ -139,6 +141,23 @@ def check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
     LAUNCHES += _LAUNCHES_PER_CALL.get(what, 1)
+
+
+def set_peer_wait_limit(seconds: float) -> None:
+    """Limit of every in-kernel wait on another GPU's flag (current device). Bounded waits that run out set the status
+    word, which the train step reads once per step; the default of 2 s suits tests, production jobs pass a longer one
+    through ``DistributedCfg.peer_wait_timeout``."""
+    rc = lib().pt_set_peer_wait_limit_ns(int(seconds * 1e9))
+    if rc != 0:
+        raise RuntimeError(f"pt_set_peer_wait_limit_ns failed with code {rc}")
+
+
+def fetch_status() -> int:
+    """Synchronise, read and clear the status word; returns the code (0 = no kernel reported anything)."""
+    v = lib().pt_status_fetch_and_clear()
+    if v < 0:
+        raise RuntimeError(f"status word unavailable ({v})")
+    return v
 
 
 def check_status() -> None:

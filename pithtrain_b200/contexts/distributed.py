@@ -9,6 +9,10 @@ local_rank: int = 0
 local_world_size: int = 1
 device: torch.device = torch.device("cpu")
 backend: str = "gloo"
+# transports of the shard-group collectives and of the context-parallel ring: "auto" = kernels over peer memory when
+# the group sits on one node with peer access, NCCL otherwise; "nccl" = always NCCL
+shard_backend: str = "auto"
+cp_backend: str = "auto"
 
 device_mesh: Any = None  # parallel.mesh.Mesh4D
 pp_group: Any = None
@@ -33,7 +37,7 @@ ep_size: int = 1
 def reset_single_process() -> None:
     """Point every field at a 1-rank world (unit tests that never call setup_distributed)."""
     g = globals()
-    g.update(rank=0, world_size=1, local_rank=0, local_world_size=1, backend="gloo",
+    g.update(rank=0, world_size=1, local_rank=0, local_world_size=1, backend="gloo", shard_backend="auto", cp_backend="auto",
              device=torch.device("cpu"), device_mesh=None,
              pp_group=None, dp_group=None, cp_group=None, ep_group=None,
              dp_cp_group=None, dp_cp_ep_group=None, dp_ep_group=None,

@@ -4,11 +4,11 @@
 // :58-70). K and V may point into another GPU's published buffer (plain, non-multicast TMA loads), which is how the
 // context-parallel ring reads a peer's block while computing on it.
 //
-//   grid  = (ceil(q tiles / NQ), Hq, B); a CTA owns NQ (two, where TMEM allows) consecutive 128-row query tiles of one
+//   grid  = (Hq * B, ceil(q tiles / NQ)); a CTA owns NQ (two, where TMEM allows) consecutive 128-row query tiles of one
 //           head and walks the key tiles they can see; CTAs with the most key tiles are scheduled first.
 //   warp 0          TMA producer : Q tiles once, then K and V tiles of 128 keys through KST-stage rings
-//   warp 1          MMA issuer   : S_t = Q_t K^T into TMEM; O_t += P_t V with P_t read from TMEM
-//   warps 2..5      softmax of tile 0, warps 6..9 softmax of tile 1: one thread per query row (tcgen05.ld 32x32b hands
+//   warps 1..NQ     MMA issuers  : one per query tile: S_t = Q_t K^T into TMEM; O_t += P_t V with P_t read from TMEM
+//   warps 4..       softmax, 4 warps per tile, one thread per query row (tcgen05.ld 32x32b hands
 //                   thread t row t of the warp's lane quarter, so row max / row sum need no shuffles). The row's 128
 //                   scores are held in registers; P is written back over S in TMEM as packed bf16 (64 columns) and
 //                   feeds the P V MMA from there, so P never touches shared memory. O is rescaled lazily (only when a
@@ -28,6 +28,15 @@ namespace pt {
 
 constexpr int AT_SLAB = 128 * 64 * 2;      // one [128 x 64] bf16 swizzle slab: 16 KB
 constexpr float AT_RESCALE_LOG2 = 8.0f;    // tolerated growth of a row maximum before O is rescaled
+#ifndef AT_SCALAR_EXP
+#define AT_SCALAR_EXP 0
+#endif
+#ifndef AT_POLY_MASK
+// Which of every 8 element pairs take the polynomial exp2 (bit i = pair i). 0: all exponentials on the special-function
+// unit. Shares of 25..75 % measured no faster on B200 at head dim 128 (the integer half of the polynomial path lands on
+// the half-rate ALU pipe), so the default is off; the path stays for head dims where the balance differs.
+#define AT_POLY_MASK 0x0u
+#endif
 
 struct AttnArgs {
   int B, Sq, Sk, Hq, Hkv;
@@ -49,12 +58,64 @@ struct AttnFwdCfg {
   static constexpr int V_BYTES = (DV / 64) * AT_SLAB;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM = NQ * Q_BYTES + KST * (K_BYTES + V_BYTES) + BAR_BYTES + 1024;
-  static constexpr int THREADS = 64 + 128 * NQ;
+  // warp group 0: producer, one MMA warp per tile, idle warps; then one warp group of four softmax warps per tile
+  static constexpr int THREADS = 128 + 128 * NQ;
   static_assert(NQ * 128 + NQ * DV <= 512, "TMEM columns");
 };
 
+
+// p = 2^(s * scale - m) for the 128 scores of a row (in registers), written back over the scores' TMEM columns as
+// packed bf16 (chunk c of 32 keys -> columns [16c, 16c+16)); returns the row sum. POLY selects which of every 8
+// element pairs are evaluated by polynomial on the FMA pipe instead of the special-function unit.
+template <uint32_t POLY>
+__device__ __forceinline__ float softmax_exp_store(const uint32_t (&sv)[128], float scale_log2, float m_use, uint32_t tS) {
+#if AT_SCALAR_EXP
+  float l4[4] = {0.f, 0.f, 0.f, 0.f};
+  const float nm = -m_use;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), scale_log2, nm));
+      const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), scale_log2, nm));
+      l4[(2 * i) & 3] += e0;
+      l4[(2 * i + 1) & 3] += e1;
+      w[i] = pack_bf16x2(e0, e1);
+    }
+    tmem_st_32x16(tS + c * 16, w);
+  }
+  return (l4[0] + l4[1]) + (l4[2] + l4[3]);
+#else
+  const uint64_t SC2 = f2_pack(scale_log2, scale_log2), NM2 = f2_pack(-m_use, -m_use);
+  uint64_t L2a = f2_pack(0.f, 0.f), L2b = L2a;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float x0, x1, e0, e1;
+      f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + 2 * i]), __uint_as_float(sv[c * 32 + 2 * i + 1])), SC2, NM2), x0, x1);
+      if (POLY & (1u << (i & 7))) {
+        exp2_poly_pair(x0, x1, e0, e1);
+      } else {
+        e0 = ex2_approx(x0);
+        e1 = ex2_approx(x1);
+      }
+      if (i & 1) L2b = f2_add(L2b, f2_pack(e0, e1)); else L2a = f2_add(L2a, f2_pack(e0, e1));
+      w[i] = pack_bf16x2(e0, e1);
+    }
+    tmem_st_32x16(tS + c * 16, w);
+  }
+  float a0, a1, b0, b1;
+  f2_unpack(L2a, a0, a1);
+  f2_unpack(L2b, b0, b1);
+  return (a0 + a1) + (b0 + b1);
+#endif
+}
+
 template <int DQK, int DV, int NQ, int KST>
-__global__ void __launch_bounds__(64 + 128 * NQ, 1)
+__global__ void __launch_bounds__(128 + 128 * NQ, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnArgs args) {
   using Cfg = AttnFwdCfg<DQK, DV, NQ, KST>;
@@ -76,8 +137,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = gridDim.x - 1 - blockIdx.x;  // heavy CTAs first (causal: the last query tiles see the most keys)
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Blocks start in linear order (x fastest): heads and batch entries run along x and query-tile pairs along y, last
+  // pair first, so that under a causal mask the CTAs with the most key tiles start first on every SM and the short
+  // ones fill the tail.
+  const int pair = gridDim.y - 1 - blockIdx.y;
+  const int h = blockIdx.x % args.Hq, b = blockIdx.x / args.Hq;
   const int hk = h / (args.Hq / args.Hkv);
   const int nK = (args.Sk + 127) / 128;
   const int row_base = b * args.Sq;
@@ -104,8 +168,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KST; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], NQ);   // every MMA warp releases a stage
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], NQ);
     }
     for (int t = 0; t < NQ; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
     *abort_flag = 0;
@@ -120,6 +184,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
+  if (NQ == 2) {
+    // 12 warps share the register file three to a scheduler (168 each). The softmax threads hold a whole score row and
+    // need independent exponentials in flight; the producer, the issuers and the idle warp need few registers.
+    // Each role's code follows its own setmaxnreg so that the compiler may use the larger budget there.
+    if (warp < 4) setmaxnreg_dec<72>();
+  }
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -170,69 +240,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!drained && args.err) atomicCAS(args.err, 0, PT_ERR_TIMEOUT_DRAIN);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp <= NQ) {
+    // ---------------------------------------------------------------- MMA issuers, one warp (one thread) per query tile
+    // A thread that issues tcgen05.mma runs nearly in lock step with the tensor core (the queue behind it is short), so
+    // every barrier wait, fence and commit of a lone issuer is tensor-core idle time. With one issuer per tile the MMAs
+    // of one tile run while the other issuer does its bookkeeping. The tiles are independent; the K / V stages are
+    // released when both issuers have committed past them.
+    const int t = warp - 1;
     if (lane == 0 && J1 > J0) {
       constexpr uint32_t IDESC_S = make_idesc(1, 1, 128, 128, false, false);
       constexpr uint32_t IDESC_O = make_idesc(1, 1, 128, DV, false, true);
+      const int lo = lo_t[t], hi = hi_t[t];
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-      int kwaited = J0 - 1, vwaited = J0 - 1;  // last key tile whose K / V arrival has been observed
-      auto act = [&](int t, int j) { return j >= lo_t[t] && j < hi_t[t]; };
-      auto issue_S = [&](int t, int j) -> bool {
+      // descriptor words of the operand tiles: a stage or a k-step moves only the low word
+      constexpr uint32_t HI = smem_desc_hi_sw128(1024);
+      const uint32_t a_lo = smem_desc_lo(smem_u32(sQ + t * Cfg::Q_BYTES), 16), k_lo0 = smem_desc_lo(smem_u32(sK), 16);
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(sV), AT_SLAB);
+      const uint32_t tS = tmem_base + t * 128, tO = tmem_base + NQ * 128 + t * DV;
+      // A stage is released through tcgen05.commit (arrives once this thread's MMAs so far have completed); an issuer
+      // whose tile does not exist (odd tile count) has no MMA to wait for and arrives directly.
+      const bool any = hi > lo;
+      auto release = [&](uint64_t* bar) { if (any) umma_commit(bar); else mbar_arrive(bar); };
+      // S_t(j) = Q_t K_j^T when the tile sees key tile j; the K stage is released either way
+      auto step_S = [&](int j) -> bool {
         const int c = j - J0, s = c % KST;
-        if (kwaited < j) {
-          if (!mbar_wait_bounded(&k_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA)) return false;
-          kwaited = j;
+        // every issuer follows the ring stage by stage, also past tiles it does not use: a stage's release counts one
+        // arrival per issuer, so nobody may run a full ring ahead
+        if (!mbar_wait_bounded(&k_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA)) return false;
+        if (j >= lo && j < hi) {
+          tc_fence_after();
+          const uint32_t b_lo = k_lo0 + s * (Cfg::K_BYTES >> 4);
+#pragma unroll
+          for (int db = 0; db < DQK / 64; ++db)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_lh(tS, a_lo + ((db * AT_SLAB + k * 32) >> 4), HI, b_lo + ((db * AT_SLAB + k * 32) >> 4), HI, IDESC_S,
+                          (db | k) != 0 ? 1u : 0u);
+          umma_commit(&s_full[t]);
         }
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + t * Cfg::Q_BYTES), k_addr = smem_u32(sK + s * Cfg::K_BYTES);
-#pragma unroll
-        for (int db = 0; db < DQK / 64; ++db)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + t * 128, make_smem_desc_sw128(q_addr + db * AT_SLAB + k * 32, 16, 1024),
-                     make_smem_desc_sw128(k_addr + db * AT_SLAB + k * 32, 16, 1024), IDESC_S, (db | k) != 0 ? 1u : 0u);
-        umma_commit(&s_full[t]);
+        release(&k_empty[s]);
         return true;
       };
-      if (ok) {
-#pragma unroll
-        for (int t = 0; t < NQ; ++t)
-          if (ok && act(t, J0)) ok = issue_S(t, J0);
-        if (ok) umma_commit(&k_empty[0]);
-      }
+      if (ok) ok = step_S(J0);
       for (int j = J0; j < J1 && ok; ++j) {
         const int c = j - J0, s = c % KST;
-#pragma unroll
-        for (int t = 0; t < NQ; ++t) {
-          if (!ok) break;
-          if (act(t, j)) {
-            ok = mbar_wait_bounded(&p_full[t], (j - lo_t[t]) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-            if (!ok) break;
-            if (vwaited < j) {
-              ok = mbar_wait_bounded(&v_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-              if (!ok) break;
-              vwaited = j;
-            }
-            tc_fence_after();
-            const uint32_t v_addr = smem_u32(sV + s * Cfg::V_BYTES);
-            const uint32_t tP = tmem_base + t * 128, tO = tmem_base + NQ * 128 + t * DV;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_f16_ts(tO, tP + k * 8, make_smem_desc_sw128(v_addr + k * 2048, AT_SLAB, 1024), IDESC_O,
-                          (j != lo_t[t] || k != 0) ? 1u : 0u);
-            if (j == hi_t[t] - 1) umma_commit(&o_done[t]);
-          }
-          if (j + 1 < J1 && act(t, j + 1)) ok = issue_S(t, j + 1);
-        }
+        ok = mbar_wait_bounded(&v_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
         if (!ok) break;
-        umma_commit(&v_empty[s]);
-        if (j + 1 < J1) umma_commit(&k_empty[(c + 1) % KST]);
+        if (j >= lo && j < hi) {
+          ok = mbar_wait_bounded(&p_full[t], (j - lo) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t b_lo = v_lo0 + s * (Cfg::V_BYTES >> 4);
+          const uint32_t acc0 = (j != lo) ? 1u : 0u;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_f16_ts_lh(tO, tS + k * 8, b_lo + ((k * 2048) >> 4), HI, IDESC_O, k != 0 ? 1u : acc0);
+          if (j == hi - 1) umma_commit(&o_done[t]);
+        }
+        release(&v_empty[s]);
+        if (j + 1 < J1) ok = step_S(j + 1);
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax (one thread per row)
-    const int t = (warp - 2) >> 2;            // query tile of this warp group
+    if (NQ == 2) setmaxnreg_inc<216>();
+    const int t = (warp - 4) >> 2;            // query tile of this warp group
     const int q = warp & 3;                   // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;              // row of the tile
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
@@ -259,14 +331,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
       tmem_ld_wait();
       const int kpos0 = j * 128;
-      if (kpos0 < lo_row || kpos0 + 127 > hi_row) {
+      const bool masked = kpos0 < lo_row || kpos0 + 127 > hi_row;
+      if (masked) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (kpos0 + i < lo_row || kpos0 + i > hi_row) sv[i] = 0xff800000u;  // -inf
       }
-      float mx = -INFINITY;
+      // row maximum: four independent chains (a thread has little other work to hide a 128-long dependency)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      for (int i = 0; i < 128; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1])));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * args.scale_log2);  // scale > 0
       // The S MMA of this step was issued after the P V MMA of the previous one, so O is stable here.
       const bool grow = m_new > m_ref + AT_RESCALE_LOG2;
@@ -288,19 +367,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        // chunk c holds keys [32c, 32c+32) -> packed bf16 columns [16c, 16c+16) of the same TMEM region
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float e0 = exp2f(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), args.scale_log2, -m_use));
-          const float e1 = exp2f(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), args.scale_log2, -m_use));
-          l += e0 + e1;
-          w[i] = pack_bf16x2(e0, e1);
-        }
-        tmem_st_32x16(tS + c * 16, w);
-      }
+      // masked tiles need exact zeros, which only the special-function path gives; the others put a share of the
+      // exponentials on the FMA pipe
+      // (the choice is made per warp: the TMEM stores inside are warp-collective)
+      if (__any_sync(0xffffffffu, masked)) l += softmax_exp_store<0u>(sv, args.scale_log2, m_use, tS);
+      else l += softmax_exp_store<AT_POLY_MASK>(sv, args.scale_log2, m_use, tS);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -380,7 +451,7 @@ int attn_fwd_launch_t(const void* q, const void* k, const void* v, const AttnArg
     configured = true;
   }
   const int nQ = (a.Sq + 127) / 128;
-  dim3 grid((nQ + NQ - 1) / NQ, a.Hq, a.B);
+  dim3 grid(a.Hq * a.B, (nQ + NQ - 1) / NQ);
   attn_fwd_kernel<DQK, DV, NQ, KST><<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

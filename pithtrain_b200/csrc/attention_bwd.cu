@@ -4,7 +4,7 @@
 // :71-87). S and dP are recomputed from Q, K, V, dO and the forward's log-sum-exp; nothing of size S x S is stored.
 //
 //   pre  : delta[b,h,r] = sum_d dO*O (fp32) and lse2 = lse * log2(e); the fp32 accumulators are zeroed by the caller
-//   main : grid = (key tiles, Hq, B). A CTA owns one 128-key tile of one query head (K, V tiles stay in shared memory)
+//   main : grid = (Hq * B, key tiles). A CTA owns one 128-key tile of one query head (K, V tiles stay in shared memory)
 //          and walks the query tiles i that can see it. Everything is computed transposed, so that a thread owns a
 //          key row and the dK / dV accumulators (rows = keys) stay in TMEM for the whole walk:
 //            S^T  = K Q_i^T              -> TMEM region R[n&1]
@@ -16,8 +16,9 @@
 //          dQ_i leaves through registers and a swizzled staging tile as a TMA reduce-add into an fp32 accumulator.
 //          The tensor core runs dP(n), dV(n), S(n+1), dK(n), dQ(n): the next S^T is issued as soon as dP^T has been
 //          read, so the exponentials of step n+1 overlap the dK / dQ MMAs of step n.
-//          warp 0 TMA producer | warp 1 MMA issuer | warps 2..9 two compute warp groups (64 query columns each)
-//          | warps 10..13 dQ reduction and the final dK / dV reduce-add (fp32, summed over the heads of a GQA group).
+//          warp 0 TMA producer | warps 1, 2 MMA issuers (S^T, dP^T | dV, dK, dQ) | warps 4..11 two compute warp groups
+//          (64 query columns each) | warps 12..15 dQ reduction and the final dK / dV reduce-add (fp32, summed over the
+//          heads of a GQA group). setmaxnreg moves registers from the first warp group to the others.
 //   post : dq = bf16(acc * scale), dk = bf16(acc * scale), dv = bf16(acc).
 //
 // Every wait is bounded (mbar_wait_bounded); on a timeout the roles leave their loops, the CTA frees its TMEM and
@@ -44,34 +45,35 @@ struct AttnBwdCfg {
   static constexpr int T_BYTES = (D / 64) * AB_SLAB;          // one [128 x D] bf16 tile
   static constexpr int DS_BYTES = 2 * AB_SLAB;                // dS^T [128 keys x 128 queries] bf16
   static constexpr int STG_BYTES = 4 * 2 * 4096;              // 4 reduce warps x 2 staging tiles of [32 x 32] fp32
+  static constexpr int STAT_BYTES = 2 * 1024;                  // two stages of lse2[128] | delta[128]
   static constexpr int BAR_BYTES = 256;
-  // K, V, Q x2, dO, dS, staging
-  static constexpr int SMEM = 5 * T_BYTES + DS_BYTES + STG_BYTES + BAR_BYTES + 1024;
-  static constexpr int THREADS = 14 * 32;
+  // K, V, Q x2, dO, dS, staging, row statistics. No slack for re-aligning the base: the kernel checks that the dynamic
+  // shared-memory window starts on a 1024-byte boundary (the swizzled tiles need it) and reports if it does not.
+  static constexpr int SMEM = 5 * T_BYTES + DS_BYTES + STG_BYTES + STAT_BYTES + BAR_BYTES;
+  static constexpr int THREADS = 16 * 32;
 };
 
-__device__ __forceinline__ float4 ldg_nc_f4(const float* p) {
-  float4 v;
-  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
-}
-
 template <int D>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(512, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                 const __grid_constant__ CUtensorMap tmDV, const AttnBwdArgs args) {
   using Cfg = AttnBwdCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {  // uniform over the CTA
+    if (threadIdx.x == 0 && args.err) atomicCAS(args.err, 0, PT_ERR_SMEM_ALIGN);
+    return;
+  }
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::T_BYTES;
   uint8_t* sQ = sV + Cfg::T_BYTES;           // two stages
   uint8_t* sDO = sQ + 2 * Cfg::T_BYTES;
   uint8_t* sDS = sDO + Cfg::T_BYTES;
   uint8_t* sStg = sDS + Cfg::DS_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStg + Cfg::STG_BYTES);
+  uint8_t* sStat = sStg + Cfg::STG_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + Cfg::STAT_BYTES);
   uint64_t* kv_full = bars;        // 1
   uint64_t* q_full = bars + 1;     // 2
   uint64_t* q_empty = bars + 3;    // 2
@@ -89,7 +91,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  // heads and batch entries along x, key tiles along y: blocks start in linear order (x fastest), so under a causal
+  // mask the key tiles with the most query tiles (the first ones) start first on every SM
+  const int j = blockIdx.y, hq = blockIdx.x % args.Hq, b = blockIdx.x / args.Hq;
   const int hk = hq / (args.Hq / args.Hkv);
   const int nQ = (args.Sq + 127) / 128;
   const int row_base = b * args.Sq, kv_base = b * args.Sk;
@@ -119,8 +123,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(do_full, 1); mbar_init(do_empty, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2); }  // both issuers release
+    mbar_init(do_full, 1); mbar_init(do_empty, 2);
     mbar_init(s_full, 1); mbar_init(dp_full, 1);
     mbar_init(p_ready, 8); mbar_init(dp_read, 8); mbar_init(ds_ready, 8);
     mbar_init(dq_full, 1); mbar_init(dq_read, 4); mbar_init(all_done, 1);
@@ -138,6 +142,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
   const uint32_t tDK = tmem_base + 256, tDV = tmem_base + 256 + D;
+  // 16 warps share the register file four to a scheduler (128 each): the producer and the issuers need few, the
+  // compute and reduction threads hold 64..128 values at a time. Each role's code follows its own setmaxnreg so that
+  // the compiler may use the larger budget there.
+  if (warp < 4) setmaxnreg_dec<56>();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -155,10 +163,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int r0 = row_base + (i_lo + n) * 128;
         ok = mbar_wait_bounded(&q_empty[st], ((n >> 1) & 1) ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
         if (!ok) break;
-        mbar_expect_tx(&q_full[st], Cfg::T_BYTES);
+        mbar_expect_tx(&q_full[st], Cfg::T_BYTES + 1024);
 #pragma unroll
         for (int db = 0; db < D / 64; ++db)
           tma_load_2d(sQ + st * Cfg::T_BYTES + db * AB_SLAB, &tmQ, &q_full[st], hq * D + 64 * db, r0);
+        {
+          const long long so = ((long long)b * args.Hq + hq) * args.Sq + (long long)(i_lo + n) * 128;
+          bulk_load_1d(sStat + st * 1024, args.lse2 + so, 512, &q_full[st]);
+          bulk_load_1d(sStat + st * 1024 + 512, args.delta + so, 512, &q_full[st]);
+        }
         ++nq_issued;
         ok = mbar_wait_bounded(do_empty, (n & 1) ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
         if (!ok) break;
@@ -183,93 +196,121 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!drained && args.err) atomicCAS(args.err, 0, PT_ERR_TIMEOUT_DRAIN);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp <= 2) {
+    // ---------------------------------------------------------------- MMA issuers
+    // A thread that issues tcgen05.mma runs nearly in lock step with the tensor core, so the waits, fences and commits
+    // of a lone issuer are tensor-core idle time. Two issuers share the work: the "front" (warp 1) issues S^T and dP^T,
+    // the "back" (warp 2) dV, dK and dQ. MMAs of one thread execute in order; every hazard between the two threads is
+    // covered by a barrier the consumer side already needs (dp_read before the next S^T, dq_read before the next dP^T,
+    // p_ready / ds_ready before dV / dK / dQ). Q and dO stages are released when both issuers have committed past them.
     if (lane == 0) {
       constexpr uint32_t IDESC_ST = make_idesc(1, 1, 128, 128, false, false);  // S^T, dP^T: both operands K-major
       constexpr uint32_t IDESC_DV = make_idesc(1, 1, 128, D, false, true);     // A in TMEM, B MN-major
       constexpr uint32_t IDESC_DK = make_idesc(1, 1, 128, D, false, true);     // A K-major smem, B MN-major
       constexpr uint32_t IDESC_DQ = make_idesc(1, 1, 128, D, true, true);      // both MN-major
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
-      auto issue_S = [&](int n) {
-        const uint32_t q_addr = smem_u32(sQ + (n & 1) * Cfg::T_BYTES);
-        const uint32_t d = tmem_base + (n & 1) * 128;
-#pragma unroll
-        for (int db = 0; db < D / 64; ++db)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(d, make_smem_desc_sw128(k_addr + db * AB_SLAB + k * 32, 16, 1024),
-                     make_smem_desc_sw128(q_addr + db * AB_SLAB + k * 32, 16, 1024), IDESC_ST, (db | k) != 0 ? 1u : 0u);
-        umma_commit(s_full);
-      };
+      // descriptor words of the operand tiles (see smem_desc_lo): "k" = read K-major (rows 128 B apart), "m" = read
+      // MN-major (the reduction index walks the rows, 64-element blocks one slab apart)
+      constexpr uint32_t HI = smem_desc_hi_sw128(1024);
+      const uint32_t k_k = smem_desc_lo(smem_u32(sK), 16), k_m = smem_desc_lo(smem_u32(sK), AB_SLAB);
+      const uint32_t v_k = smem_desc_lo(smem_u32(sV), 16);
+      const uint32_t do_k = smem_desc_lo(smem_u32(sDO), 16), do_m = smem_desc_lo(smem_u32(sDO), AB_SLAB);
+      const uint32_t ds_k = smem_desc_lo(smem_u32(sDS), 16), ds_m = smem_desc_lo(smem_u32(sDS), AB_SLAB);
+      const uint32_t q_k0 = smem_desc_lo(smem_u32(sQ), 16), q_m0 = smem_desc_lo(smem_u32(sQ), AB_SLAB);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-      if (ok) ok = mbar_wait_bounded(&q_full[0], 0, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-      if (ok) { tc_fence_after(); issue_S(0); }
-      for (int n = 0; n < N && ok; ++n) {
-        const uint32_t ph = n & 1;
-        const uint32_t tRS = tmem_base + (n & 1) * 128, tRP = tmem_base + (1 - (n & 1)) * 128;
-        const uint32_t q_addr = smem_u32(sQ + (n & 1) * Cfg::T_BYTES);
-        ok = mbar_wait_bounded(do_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        if (n > 0) {
-          ok = mbar_wait_bounded(dq_read, (n - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+      if (warp == 1) {
+        // ------------------------------------------------ front: S^T(n+1) and dP^T(n)
+        auto issue_S = [&](int n) {
+          const uint32_t q_k = q_k0 + (n & 1) * (Cfg::T_BYTES >> 4);
+          const uint32_t d = tmem_base + (n & 1) * 128;
+#pragma unroll
+          for (int db = 0; db < D / 64; ++db)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_lh(d, k_k + ((db * AB_SLAB + k * 32) >> 4), HI, q_k + ((db * AB_SLAB + k * 32) >> 4), HI, IDESC_ST,
+                          (db | k) != 0 ? 1u : 0u);
+          umma_commit(s_full);
+          umma_commit(&q_empty[n & 1]);  // this issuer's share of the release of Q(n)
+        };
+        if (ok) ok = mbar_wait_bounded(&q_full[0], 0, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+        if (ok) { tc_fence_after(); issue_S(0); }
+        for (int n = 0; n < N && ok; ++n) {
+          const uint32_t ph = n & 1;
+          const uint32_t tRP = tmem_base + (1 - (n & 1)) * 128;
+          ok = mbar_wait_bounded(do_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
+          if (n > 0) {
+            ok = mbar_wait_bounded(dq_read, (n - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          // dP^T = V dO^T
+#pragma unroll
+          for (int db = 0; db < D / 64; ++db)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_lh(tRP, v_k + ((db * AB_SLAB + k * 32) >> 4), HI, do_k + ((db * AB_SLAB + k * 32) >> 4), HI, IDESC_ST,
+                          (db | k) != 0 ? 1u : 0u);
+          umma_commit(dp_full);
+          umma_commit(do_empty);  // this issuer's share of the release of dO(n)
+          // next S^T into the region dP^T has just left
+          ok = mbar_wait_bounded(dp_read, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          if (n + 1 < N) {
+            ok = mbar_wait_bounded(&q_full[(n + 1) & 1], ((n + 1) >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            issue_S(n + 1);
+          }
         }
-        tc_fence_after();
-        // dP^T = V dO^T
-#pragma unroll
-        for (int db = 0; db < D / 64; ++db)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tRP, make_smem_desc_sw128(v_addr + db * AB_SLAB + k * 32, 16, 1024),
-                     make_smem_desc_sw128(do_addr + db * AB_SLAB + k * 32, 16, 1024), IDESC_ST, (db | k) != 0 ? 1u : 0u);
-        umma_commit(dp_full);
-        // dV += P^T dO  (P^T packed bf16 in TMEM: query columns 0..63 at +0, 64..127 at +64)
-        ok = mbar_wait_bounded(p_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16_ts(tDV, tRS + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc_sw128(do_addr + k * 2048, AB_SLAB, 1024), IDESC_DV,
-                      (n | k) != 0 ? 1u : 0u);
-        umma_commit(do_empty);
-        // next S^T into the region dP^T has just left
-        ok = mbar_wait_bounded(dp_read, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        if (n + 1 < N) {
-          ok = mbar_wait_bounded(&q_full[(n + 1) & 1], ((n + 1) >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+      } else {
+        // ------------------------------------------------ back: dV(n), dK(n), dQ(n)
+        for (int n = 0; n < N && ok; ++n) {
+          const uint32_t ph = n & 1;
+          const uint32_t tRS = tmem_base + (n & 1) * 128;
+          const uint32_t q_m = q_m0 + (n & 1) * (Cfg::T_BYTES >> 4);
+          const uint32_t accn = n != 0 ? 1u : 0u;
+          // dV += P^T dO  (P^T packed bf16 in TMEM: query columns 0..63 at +0, 64..127 at +64)
+          ok = mbar_wait_bounded(do_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          ok = mbar_wait_bounded(p_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
-          issue_S(n + 1);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_f16_ts_lh(tDV, tRS + (k >> 2) * 64 + (k & 3) * 8, do_m + ((k * 2048) >> 4), HI, IDESC_DV, k != 0 ? 1u : accn);
+          umma_commit(do_empty);
+          // dK += dS^T Q ; dQ = dS K
+          ok = mbar_wait_bounded(&q_full[n & 1], (n >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          ok = mbar_wait_bounded(ds_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_lh(tDK, ds_k + ((g * AB_SLAB + k * 32) >> 4), HI, q_m + (((g * 4 + k) * 2048) >> 4), HI, IDESC_DK,
+                          (g | k) != 0 ? 1u : accn);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_f16_lh(tRS, ds_m + ((k * 2048) >> 4), HI, k_m + ((k * 2048) >> 4), HI, IDESC_DQ, k != 0 ? 1u : 0u);
+          umma_commit(dq_full);
+          umma_commit(&q_empty[n & 1]);
         }
-        // dK += dS^T Q ; dQ = dS K
-        ok = mbar_wait_bounded(ds_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tDK, make_smem_desc_sw128(ds_addr + g * AB_SLAB + k * 32, 16, 1024),
-                     make_smem_desc_sw128(q_addr + (g * 4 + k) * 2048, AB_SLAB, 1024), IDESC_DK, (n | g | k) != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16(tRS, make_smem_desc_sw128(ds_addr + k * 2048, AB_SLAB, 1024),
-                   make_smem_desc_sw128(k_addr + k * 2048, AB_SLAB, 1024), IDESC_DQ, k != 0 ? 1u : 0u);
-        umma_commit(dq_full);
-        umma_commit(&q_empty[n & 1]);
+        if (ok) umma_commit(all_done);
       }
-      if (ok) umma_commit(all_done);
     }
-  } else if (warp < 10) {
+  } else if (warp == 3) {
+    // idle: completes the first warp group
+  } else if (warp < 12) {
     // ---------------------------------------------------------------- compute: thread = key row, 64 query columns
-    const int g = (warp - 2) >> 2;            // column half
+    setmaxnreg_inc<152>();
+    const int g = (warp - 4) >> 2;            // column half
     const int qd = warp & 3;                  // TMEM lane quarter
     const int r = qd * 32 + lane;             // key row of the tile
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const int kp = k_first + r;               // key position within the batch entry
     const bool key_valid = kp < args.Sk;
-    const long long stat_base = ((long long)b * args.Hq + hq) * args.Sq;
     uint8_t* ds_row = sDS + g * AB_SLAB + r * 128;
     for (int n = 0; n < N; ++n) {
       const int i = i_lo + n;
@@ -282,37 +323,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (args.causal) need_mask = need_mask || (args.q_off + i * 128 < k_first + 127);
       if (args.row_lo) need_mask = need_mask || (args.row_lo[row_base + min(i * 128 + 127, args.Sq - 1)] > k_first);
       int good = 1;
-      if (lane == 0) good = mbar_wait_bounded(s_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+      if (lane == 0) {
+        good = mbar_wait_bounded(s_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+        // the row statistics arrived with Q (already complete: S^T has been computed from it)
+        if (good) good = mbar_wait_bounded(&q_full[n & 1], (n >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+      }
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) break;
       tc_fence_after();
+      const float* st_lse = reinterpret_cast<const float*>(sStat + (n & 1) * 1024) + g * 64;
+      const float* st_del = st_lse + 128;
       uint32_t pk[32];  // P^T of my row, 64 query columns, packed bf16
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32];
-        tmem_ld_32x32(tRS + c * 32, sv);
-        float ls[32];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float4 v4 = ldg_nc_f4(args.lse2 + stat_base + q0 + c * 32 + u * 4);
-          ls[4 * u] = v4.x; ls[4 * u + 1] = v4.y; ls[4 * u + 2] = v4.z; ls[4 * u + 3] = v4.w;
-        }
+      {
+        uint32_t sv[64];
+        tmem_ld_32x32(tRS, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32(tRS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
-        float p[32];
 #pragma unroll
-        for (int x = 0; x < 32; ++x) p[x] = exp2f(fmaf(__uint_as_float(sv[x]), args.scale_log2, -ls[x]));
-        if (need_mask) {
+        for (int u = 0; u < 16; ++u) {
+          const float4 ls = *reinterpret_cast<const float4*>(st_lse + u * 4);
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y));
+          float p2 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z));
+          float p3 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 3]), args.scale_log2, -ls.w));
+          if (need_mask) {
+            const int qr = q0 + 4 * u;
+            const float pv[4] = {p0, p1, p2, p3};
+            float po[4];
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int qr = q0 + c * 32 + x;
-            bool vis = key_valid && qr < args.Sq;
-            if (args.causal) vis = vis && kp <= args.q_off + qr;
-            if (args.row_lo && vis) vis = kp >= args.row_lo[row_base + qr];
-            if (!vis) p[x] = 0.f;
+            for (int x = 0; x < 4; ++x) {
+              bool vis = key_valid && qr + x < args.Sq;
+              if (args.causal) vis = vis && kp <= args.q_off + qr + x;
+              if (args.row_lo && vis) vis = kp >= args.row_lo[row_base + qr + x];
+              po[x] = vis ? pv[x] : 0.f;
+            }
+            p0 = po[0]; p1 = po[1]; p2 = po[2]; p3 = po[3];
           }
+          pk[2 * u] = pack_bf16x2(p0, p1);
+          pk[2 * u + 1] = pack_bf16x2(p2, p3);
         }
-#pragma unroll
-        for (int x = 0; x < 16; ++x) pk[c * 16 + x] = pack_bf16x2(p[2 * x], p[2 * x + 1]);
       }
       // both column halves of my row have been read: P^T may overwrite the first 32 columns of my S^T half
       tmem_st_32x32(tRS, pk);
@@ -325,37 +374,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t dp[32];
-        tmem_ld_32x32(tRP + c * 32, dp);
-        float dl[32];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float4 v4 = ldg_nc_f4(args.delta + stat_base + q0 + c * 32 + u * 4);
-          dl[4 * u] = v4.x; dl[4 * u + 1] = v4.y; dl[4 * u + 2] = v4.z; dl[4 * u + 3] = v4.w;
-        }
+      {
+        uint32_t dp[64];
+        tmem_ld_32x32(tRP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+        tmem_ld_32x32(tRP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
         tmem_ld_wait();
-        if (c == 1) {
-          // dP^T has left TMEM: the next S^T may be issued into this region
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(dp_read);
-        }
-        uint32_t w[16];
+        // dP^T has left TMEM: the next S^T may be issued into this region
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dp_read);
+        // 64 query columns = 8 chunks of 16 bytes in my 128-byte row of the dS^T tile
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const float2 pp = unpack_bf16x2(pk[c * 16 + x]);
-          const float d0 = pp.x * (__uint_as_float(dp[2 * x]) - dl[2 * x]);
-          const float d1 = pp.y * (__uint_as_float(dp[2 * x + 1]) - dl[2 * x + 1]);
-          w[x] = pack_bf16x2(d0, d1);
-        }
-        // 32 query columns = 4 chunks of 16 bytes; chunk index within my 128-byte row is c*4 + t
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
+        for (int t = 0; t < 8; ++t) {
+          const float4 da = *reinterpret_cast<const float4*>(st_del + t * 8);
+          const float4 db = *reinterpret_cast<const float4*>(st_del + t * 8 + 4);
+          const float2 pa = unpack_bf16x2(pk[4 * t]), pb = unpack_bf16x2(pk[4 * t + 1]);
+          const float2 pc = unpack_bf16x2(pk[4 * t + 2]), pd = unpack_bf16x2(pk[4 * t + 3]);
           uint4 v4;
-          v4.x = w[4 * t]; v4.y = w[4 * t + 1]; v4.z = w[4 * t + 2]; v4.w = w[4 * t + 3];
-          *reinterpret_cast<uint4*>(ds_row + (((c * 4 + t) ^ (r & 7)) << 4)) = v4;
+          v4.x = pack_bf16x2(pa.x * (__uint_as_float(dp[8 * t + 0]) - da.x), pa.y * (__uint_as_float(dp[8 * t + 1]) - da.y));
+          v4.y = pack_bf16x2(pb.x * (__uint_as_float(dp[8 * t + 2]) - da.z), pb.y * (__uint_as_float(dp[8 * t + 3]) - da.w));
+          v4.z = pack_bf16x2(pc.x * (__uint_as_float(dp[8 * t + 4]) - db.x), pc.y * (__uint_as_float(dp[8 * t + 5]) - db.y));
+          v4.w = pack_bf16x2(pd.x * (__uint_as_float(dp[8 * t + 6]) - db.z), pd.y * (__uint_as_float(dp[8 * t + 7]) - db.w));
+          *reinterpret_cast<uint4*>(ds_row + ((t ^ (r & 7)) << 4)) = v4;
         }
       }
       fence_proxy_async_smem();
@@ -364,9 +404,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ---------------------------------------------------------------- dQ reduction, then dK / dV
+    setmaxnreg_inc<152>();
     const int qd = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    uint8_t* stg = sStg + (warp - 10) * 8192;
+    uint8_t* stg = sStg + (warp - 12) * 8192;
     int slot = 0;
     auto stage_out = [&](const uint32_t (&v)[32], const CUtensorMap* tm, int x, int y) {
       uint8_t* st = stg + slot * 4096;
@@ -518,7 +559,7 @@ int attn_bwd_launch_t(const void* q, const void* k, const void* v, const void* o
   }
   a.lse2 = lse2;
   a.delta = delta;
-  dim3 grid((a.Sk + 127) / 128, a.Hq, a.B);
+  dim3 grid(a.Hq * a.B, (a.Sk + 127) / 128);
   attn_bwd_kernel<D><<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, tmDK, tmDV, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

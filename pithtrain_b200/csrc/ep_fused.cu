@@ -16,6 +16,7 @@
 #include "elementwise.cuh"
 #include "host_common.h"
 #include "ptx.cuh"
+#include "peer_wait.cuh"
 
 namespace pt {
 
@@ -63,7 +64,7 @@ __device__ __forceinline__ bool wait_ge_bounded(const unsigned* p, unsigned want
     if ((it & 255u) == 255u) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > PT_WAIT_LIMIT_NS) {
+      if (now - t0 > pt_peer_wait_limit_ns) {
         if (err) atomicCAS(err, 0, PT_ERR_TIMEOUT_PEER);
         return false;
       }
@@ -316,3 +317,6 @@ PT_API int pt_ep_ack(const void* chan, int slot, unsigned epoch, void* stream_) 
   ep_ack_kernel<<<1, EP_MAX, 0, (cudaStream_t)stream_>>>(c, slot, epoch);
   return (int)cudaGetLastError();
 }
+
+// Sets this translation unit's copy of the peer-wait limit on the current device (see peer_wait.cuh).
+extern "C" int pt_ep_set_wait_limit(unsigned long long ns) { return pt::set_peer_wait_limit_here(ns); }

@@ -20,6 +20,7 @@
 
 #include "host_common.h"
 #include "ptx.cuh"
+#include "peer_wait.cuh"
 
 namespace pt {
 namespace fsdp {
@@ -57,7 +58,7 @@ __device__ bool wait_ge_bounded(const unsigned* p, unsigned want, int* err) {
     if ((it & 255u) == 255u) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > PT_WAIT_LIMIT_NS) {
+      if (now - t0 > pt_peer_wait_limit_ns) {
         if (err) atomicCAS(err, 0, PT_ERR_TIMEOUT_PEER);
         return false;
       }
@@ -252,3 +253,6 @@ PT_API int pt_fsdp_wait_params(const void* chan, unsigned epoch, void* stream) {
                                                                    pt::device_status_word());
   return (int)cudaGetLastError();
 }
+
+// Sets this translation unit's copy of the peer-wait limit on the current device (see peer_wait.cuh).
+extern "C" int pt_fsdp_set_wait_limit(unsigned long long ns) { return pt::set_peer_wait_limit_here(ns); }

@@ -134,3 +134,14 @@ PT_API int pt_status_fetch_and_clear() {
 }
 
 PT_API int pt_sm_count() { return pt::sm_count(); }
+
+extern "C" int pt_ep_set_wait_limit(unsigned long long ns);
+extern "C" int pt_fsdp_set_wait_limit(unsigned long long ns);
+extern "C" int pt_symm_set_wait_limit(unsigned long long ns);
+
+// Limit (nanoseconds) of every wait on another GPU's flag, on the current device; the default is 2 s.
+PT_API int pt_set_peer_wait_limit_ns(long long ns) {
+  if (ns <= 0) return -2;
+  const unsigned long long v = static_cast<unsigned long long>(ns);
+  return (pt_ep_set_wait_limit(v) | pt_fsdp_set_wait_limit(v) | pt_symm_set_wait_limit(v)) == 0 ? 0 : -1;
+}

@@ -28,7 +28,9 @@ extern "C" {
 // Returns 0 on success, -1 for invalid arguments, -2 when E exceeds
 // PT_ROUTE_SORT_NOALLOC_MAX_EXPERTS (a message goes to stderr), or a cudaError_t value.
 // No cudaMalloc / cudaFree / allocating library routine is called. If the rows do not fit in
-// `r_cap`, nothing is written past it and offs[E] > r_cap tells the caller so.
+// `r_cap`, nothing is written past it and offs[E] > r_cap tells the caller so; in that case check
+// offs[E] before reading slot_of_row: the rows of the first group that does not fit are left
+// unwritten (neither a slot nor -1), so the contents of slot_of_row are unspecified.
 //
 // The first call on a device resolves the device address of the static scratch
 // (cudaGetSymbolAddress); make that call once per device before starting any stream capture.

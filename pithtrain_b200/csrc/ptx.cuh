@@ -19,6 +19,7 @@ enum : int {
   PT_ERR_TIMEOUT_PEER = 4,
   PT_ERR_CAPACITY = 5,
   PT_ERR_TIMEOUT_DRAIN = 6,
+  PT_ERR_SMEM_ALIGN = 7,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -87,6 +88,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Warp-collective form: lane 0 polls, the outcome is broadcast, so the whole warp leaves the wait together and its
+// control flow stays uniform (the single-thread MMA issue below is then the only predicated region).
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                       int* err, int code) {
+  int good = 1;
+  if ((threadIdx.x & 31) == 0) good = mbar_wait_bounded(bar, parity, abort_flag, err, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, good, 0) != 0;
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ----------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies; loads complete on an mbarrier, stores use bulk groups)
 // ----------------------------------------------------------------------------------------------
@@ -119,6 +139,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x,
                                              int y) {
@@ -293,6 +320,38 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// The same descriptor split into its two 32-bit words, so that an MMA loop advances the operand address with one
+// 32-bit add (a single thread issues every MMA of a CTA, so the instructions spent per MMA bound the issue rate):
+//   lo = (addr >> 4) | (lbo >> 4) << 16, hi = (sbo >> 4) | version | layout.  lo + (byte_offset >> 4) moves the start
+// address; shared-memory addresses stay below 2^18, so the sum never reaches the lbo field.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ void umma_f16_lh(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_lh(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format  [15] A MN-major  [16] B MN-major
 //   [17,23) N >> 3            [24,29) M >> 4
@@ -302,6 +361,63 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Register rebalancing between warp groups (four consecutive warps, all of which execute the instruction): roles
+// that only wait and issue give registers up, the math warps take them.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// ----------------------------------------------------------------------------------------------
+// packed fp32 pairs (Blackwell FFMA2 / FADD2: one instruction for two lanes of fp32 math)
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t r, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x on the special-function unit, one MUFU.EX2 and nothing else (exp2f wraps it in range handling for denormal
+// results, which flush-to-zero makes unnecessary here).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for a pair without the special-function unit: round-to-nearest split x = n + f, |f| <= 0.5, degree-3 polynomial
+// for 2^f (relative error 7.5e-5, below bf16 resolution), exponent added with integer arithmetic. x is clamped at
+// -126, where the result is ~1.2e-38 instead of 0; callers that need exact zeros use ex2.approx for those elements.
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& e0, float& e1) {
+  const uint64_t X = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t FI = f2_add(X, f2_pack(12582912.f, 12582912.f));
+  const uint64_t Nn = f2_add(FI, f2_pack(-12582912.f, -12582912.f));
+  const uint64_t F = f2_fma(Nn, f2_pack(-1.f, -1.f), X);
+  uint64_t P = f2_fma(F, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
+  P = f2_fma(P, F, f2_pack(0.6932609677f, 0.6932609677f));
+  P = f2_fma(P, F, f2_pack(0.9999280572f, 0.9999280572f));
+  float p0, p1, fi0, fi1;
+  f2_unpack(P, p0, p1);
+  f2_unpack(FI, fi0, fi1);
+  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(fi0) << 23));
+  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(fi1) << 23));
 }
 
 // ----------------------------------------------------------------------------------------------

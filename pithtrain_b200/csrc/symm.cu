@@ -52,6 +52,7 @@ PT_API int pt_can_access_peer(int dev, int peer) {
 // library's status word (code PT_ERR_TIMEOUT_PEER).
 // ----------------------------------------------------------------------------------------------
 #include "ptx.cuh"
+#include "peer_wait.cuh"
 
 namespace pt {
 namespace symm {
@@ -86,7 +87,7 @@ __global__ void wait_kernel(const unsigned* ctl, int index, int count, unsigned 
     if ((it & 255u) == 255u) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > PT_WAIT_LIMIT_NS) {
+      if (now - t0 > pt_peer_wait_limit_ns) {
         if (err) atomicCAS(err, 0, PT_ERR_TIMEOUT_PEER);
         return;
       }
@@ -153,3 +154,6 @@ PT_API int pt_symm_copy(void* dst, const void* src, long long bytes, int max_cta
                                                                         reinterpret_cast<const uint4*>(src), nvec);
   return (int)cudaGetLastError();
 }
+
+// Sets this translation unit's copy of the peer-wait limit on the current device (see peer_wait.cuh).
+extern "C" int pt_symm_set_wait_limit(unsigned long long ns) { return pt::set_peer_wait_limit_here(ns); }

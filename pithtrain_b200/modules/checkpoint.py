@@ -296,8 +296,14 @@ def save_training_checkpoint(cfg) -> Path:
     return path
 
 
-def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=()) -> bool:
-    """Load checkpoint ``path`` into live objects; returns True when optimizer state was present."""
+def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=(), strict: bool = True) -> bool:
+    """Load checkpoint ``path`` into live objects; returns True when optimizer state was present.
+
+    ``strict`` (default): every parameter and persistent buffer of the live model must be in the checkpoint, as with
+    the reference's ``dcp.load`` through its ``AppState`` (pithtrain/tasks/pretrain_lm.py:308-313); a checkpoint of a
+    different architecture, expert count or depth raises ``KeyError`` instead of leaving the missing tensors at their
+    random initialisation. A full checkpoint that lacks optimizer state for a parameter this rank owns is reported
+    with a warning. ``strict=False`` loads what is there."""
     import torch.distributed.checkpoint as dcp
     from torch.distributed.checkpoint import FileSystemReader
 
@@ -306,11 +312,16 @@ def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=()) -> boo
     # model: load in place into (views of) the live parameters; tolerate missing keys
     targets = to_canonical_model(dict(model.state_dict()), model)
     want_model = {k: v for k, v in targets.items() if ("app.model." + k) in md}
+    missing = sorted(k for k in targets if ("app.model." + k) not in md)
+    if missing and strict:
+        raise KeyError(f"checkpoint {path} lacks {len(missing)} of the model's {len(targets)} tensors "
+                       f"(first: {missing[:5]}); pass strict=False to load the rest")
     request: Dict[str, Any] = {"app": {"model": want_model}}
     optim_req: Dict[str, Dict[str, Any]] = {}
     if not model_only and optimizers:
         names = _param_names(model)
         prefix = "app.optimizer.state."
+        no_state: List[str] = []
         by_fqn: Dict[str, List[str]] = {}
         for k in md:
             if k.startswith(prefix):
@@ -326,6 +337,8 @@ def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=()) -> boo
                     keys = (canonical_expert_keys(name, p.shape[0], _ep_rank()) if is_stacked_expert_key(name)
                             else [strip_prefix(name)])
                     for ck in keys:
+                        if ck not in by_fqn:
+                            no_state.append(ck)
                         for field in by_fqn.get(ck, []):
                             m = md[prefix + ck + "." + field]
                             if hasattr(m, "size"):
@@ -333,6 +346,9 @@ def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=()) -> boo
                             else:
                                 optim_req.setdefault(ck, {})[field] = None
         request["app"]["optimizer"] = {"state": optim_req}
+        if no_state and by_fqn:
+            logging.stdout.warning("Load checkpoint: no optimizer state for %d owned parameters (first: %s); "
+                                   "they restart from empty state" % (len(no_state), no_state[:3]), rank=None)
         for key, holder, name in (("app.optimizer.param_groups", request["app"]["optimizer"], "param_groups"),
                                   ("app.scheduler", request["app"], "scheduler")):
             if key in md and hasattr(md[key], "size"):

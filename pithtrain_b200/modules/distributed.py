@@ -13,7 +13,7 @@ import sys
 import threading
 from dataclasses import dataclass
 from datetime import timedelta
-from typing import Literal
+from typing import Literal, Optional
 
 import torch
 import torch.distributed as dist
@@ -36,6 +36,19 @@ class DistributedCfg(SlottedDefault):
     """"auto" picks nccl when CUDA is available and gloo otherwise."""
     ep_backend: Literal["auto", "nccl", "fused"] = "auto"
     """Expert-parallel transport: NCCL all-to-all (baseline) or the fused peer-memory kernels."""
+    shard_backend: Literal["auto", "nccl"] = "auto"
+    """Gradient reduce-scatter and parameter publication of a shard group: kernels over peer memory on one node
+    ("auto"), or NCCL always (the baseline, and what groups that span nodes use anyway)."""
+    cp_backend: Literal["auto", "nccl"] = "auto"
+    """Context-parallel ring: publish-and-pull over peer memory ("auto") or hop-by-hop NCCL send/recv."""
+    ep_capacity_factor: Optional[float] = None
+    """Receive capacity of the fused expert-parallel transport. None (default): the exact worst case, ``ep * m`` rows
+    per micro-batch of ``m`` tokens, which no routing can overflow. A number opts into a smaller buffer of that
+    multiple of the expected de-duplicated volume; an overflow then fails the step loudly (status word)."""
+    peer_wait_timeout: timedelta = timedelta(seconds=60)
+    """Limit of every in-kernel wait on another GPU's flag (peer-memory transports). A wait that runs out sets the
+    device status word; the train step reads it once per step and every rank raises ``KernelStatusError`` before
+    the step's result is kept. Long enough for a rank stalled in data loading or first-step initialisation."""
 
 
 def setup_torch_runtime() -> None:
@@ -67,6 +80,10 @@ def setup_default_process_group(cfg: DistributedCfg) -> None:
         os.environ["TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC"] = str(int(cfg.timeout.total_seconds()))
         torch.cuda.set_device(distributed.local_rank)
         distributed.device = torch.device("cuda", distributed.local_rank)
+        from .. import _native
+
+        if _native.available():
+            _native.set_peer_wait_limit(cfg.peer_wait_timeout.total_seconds())
     else:
         distributed.device = torch.device("cuda", distributed.local_rank) if use_cuda and backend != "gloo" else torch.device("cpu")
 
@@ -140,4 +157,5 @@ def setup_distributed(cfg: object, failfast: bool = True) -> None:
     setup_default_process_group(cfg.distributed)
     if failfast and "RANK" in os.environ and os.environ.get("PITHTRAIN_NO_FAILFAST") != "1":
         setup_failfast_excepthook()
+    distributed.shard_backend, distributed.cp_backend = cfg.distributed.shard_backend, cfg.distributed.cp_backend
     setup_device_mesh(cfg.distributed)

@@ -308,7 +308,7 @@ def setup_model(cfg: TrainingCfg, distributed_cfg: Any) -> None:
         raise ValueError(f"sequence_length ({cfg.sequence_length}) must be divisible by 2 * context_parallel_size "
                          f"({2 * cp}): zigzag ring attention splits the sequence into 2*cp equal blocks")
     ModelClass = model_class_for(config)
-    ep_mod.setup_exchange(getattr(distributed_cfg, "ep_backend", "auto"))
+    ep_mod.setup_exchange(getattr(distributed_cfg, "ep_backend", "auto"), getattr(distributed_cfg, "ep_capacity_factor", None))
 
     dtype = torch.bfloat16 if cfg.param_dtype == "bf16" else torch.float32
     prev = torch.get_default_dtype()

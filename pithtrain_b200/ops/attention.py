@@ -2,7 +2,8 @@
 per-head sinks, asymmetric q/v head dims (MLA) and packed sequences.
 
 ``attention(q, k, v, ...)`` returns ``out[B,S,Hq,Dv]``; ``attention_with_lse`` also returns the
-log-sum-exp ``[B,Hq,S]`` that ring attention merges on. The feature set is that of the reference's
+log-sum-exp ``[B,Hq,S]`` that ring attention merges on. On GPUs the work is done by the tcgen05 kernels of
+``csrc/attention.cu`` / ``csrc/attention_bwd.cu``. The feature set is that of the reference's
 FlashAttention-4 wrapper (pithtrain/operators/flash_attn_v4.py:17-99): ``causal``,
 ``window=(left, 0)``, ``learnable_sink``, ``cu_seqlens``.
 ``attention_ref`` is the fp32 oracle.
@@ -112,94 +113,20 @@ def attention_window_blocked(q, k, v, window_left: int, scale=None, sinks=None, 
     return out.permute(0, 3, 4, 1, 2, 5).reshape(B, S, Hq, Dv).to(q.dtype)
 
 
-class _SinkFlash(torch.autograd.Function):
-    """Causal attention with per-head sinks on the library flash kernel: the kernel's log-sum-exp is extended by
-    the sink term and the output rescaled; the backward runs the library backward against the rescaled output and
-    the extended log-sum-exp (the same identity ring attention uses for blocks)."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, sinks, scale):
-        from .ring_attention import _lib_block_fwd
-
-        out, lse = _lib_block_fwd(q, k, v, scale, True)  # fp32 out [B,S,H,D], lse [B,H,S]
-        tot = torch.logaddexp(lse, sinks.float().view(1, -1, 1))
-        out = (out * torch.exp(lse - tot).permute(0, 2, 1).unsqueeze(-1)).to(q.dtype)
-        ctx.save_for_backward(q, k, v, sinks, out, tot)
-        ctx.scale = scale
-        return out
-
-    @staticmethod
-    def backward(ctx, do):
-        from .ring_attention import _lib_block_bwd
-
-        q, k, v, sinks, out, tot = ctx.saved_tensors
-        dq, dk, dv = _lib_block_bwd(do, q, k, v, out, tot, ctx.scale, True)
-        delta = (do.float() * out.float()).sum(-1).permute(0, 2, 1)  # B,H,S
-        d_sinks = -(torch.exp(sinks.float().view(1, -1, 1) - tot) * delta).sum((0, 2)).to(sinks.dtype)
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), d_sinks, None
-
-
-_HOST_BOUNDS: dict = {}
-
-
-def _document_bounds(cu_seqlens: torch.Tensor, total: int):
-    """Host copy of the document boundaries of a packed sequence (read back once per tensor)."""
-    key = (cu_seqlens.data_ptr(), cu_seqlens._version, int(cu_seqlens.numel()), total)
-    b = _HOST_BOUNDS.get(key)
-    if b is None:
-        vals = [int(x) for x in cu_seqlens.tolist()]
-        b = sorted(set([0] + [x for x in vals if 0 < x < total] + [total]))
-        if len(_HOST_BOUNDS) > 256:
-            _HOST_BOUNDS.clear()
-        _HOST_BOUNDS[key] = b
-    return b
-
-
-# Full causal attention with sinks through the library flash kernel (GPU only).
-SINK_FLASH = True
-
-
-def attention_per_document(q, k, v, cu_seqlens: torch.Tensor, scale=None, sinks=None, inner=None) -> torch.Tensor:
-    """Causal attention of a packed sequence, one call of ``inner`` (default :func:`attention`) per document."""
-    inner = inner or attention
-    bounds = _document_bounds(cu_seqlens, q.shape[1])
-    parts = [inner(q[:, a:b], k[:, a:b], v[:, a:b], True, scale, None, sinks, None) for a, b in zip(bounds[:-1], bounds[1:])]
-    return torch.cat(parts, dim=1)
-
-
-def _sdpa_ok(q, k, v, window_left, sinks, cu_seqlens) -> bool:
-    return (q.is_cuda and window_left is None and sinks is None and cu_seqlens is None
-            and q.dtype in (torch.bfloat16, torch.float16) and q.shape[-1] == v.shape[-1])
-
-
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
               scale: Optional[float] = None, window_left: Optional[int] = None,
               sinks: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 tensors on a GPU run on the framework's own tcgen05 kernels (``ops/attention_native.py``: every mask and
+    head dim the model families use); everything else (CPU, fp32, other head dims) on the fp32 math, in the blocked
+    O(S * window) form for long sliding-window sequences."""
     from . import attention_native
 
     if attention_native.supported(q, k, v, causal, window_left, sinks, cu_seqlens):
         return attention_native.attention(q, k, v, causal, scale, window_left, sinks, cu_seqlens)
-    if _sdpa_ok(q, k, v, window_left, sinks, cu_seqlens):
-        Hq, Hkv = q.shape[2], k.shape[2]
-        out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                             is_causal=causal, scale=scale, enable_gqa=(Hq != Hkv))
-        return out.transpose(1, 2)
     S = q.shape[1]
     if causal and window_left is not None and window_left >= 0 and S == k.shape[1] and S % 128 == 0 and S > 2 * (window_left + 128):
-        # sliding window (GPT-OSS): blocked evaluation, O(S * window) memory and work instead of O(S^2)
         seg = segments_from_cu_seqlens(cu_seqlens, S) if cu_seqlens is not None else None
         return attention_window_blocked(q, k, v, window_left, scale, sinks, seg)
-    if (causal and window_left is None and cu_seqlens is not None and S == k.shape[1]
-            and _sdpa_ok(q, k, v, None, sinks, None)):
-        # packed sequences: documents do not see one another, so each runs on the library kernel on its own
-        return attention_per_document(q, k, v, cu_seqlens, scale, sinks)
-    if (causal and window_left is None and cu_seqlens is None and sinks is not None and SINK_FLASH
-            and _sdpa_ok(q, k, v, None, None, None) and S == k.shape[1]):
-        from . import ring_attention as R
-
-        if R._lib_block_ok(q, k, v):
-            sc = scale if scale is not None else q.shape[-1] ** -0.5
-            return _SinkFlash.apply(q, k, v, sinks, sc)
     return attention_ref(q, k, v, causal, scale, window_left, sinks, cu_seqlens)
 
 

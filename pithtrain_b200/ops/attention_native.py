@@ -138,7 +138,7 @@ class _Attention(torch.autograd.Function):
         q, k, v, out, lse, sinks, row_lo = ctx.saved_tensors
         sinks = sinks if ctx.has_sinks else None
         row_lo = row_lo if ctx.has_lo else None
-        if (q.shape[-1], v.shape[-1]) in _BWD_DIMS:
+        if (q.shape[-1], v.shape[-1]) in _BWD_DIMS and q.shape[1] % 4 == 0:  # row statistics move in 16-byte pieces
             dq, dk, dv, delta = backward(do, q, k, v, out, lse, ctx.scale, ctx.causal, ctx.q_off, row_lo)
         else:
             dq, dk, dv, delta = _math_backward(do, q, k, v, out, lse, ctx.scale, ctx.causal, ctx.q_off, row_lo)

@@ -229,8 +229,9 @@ def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------
 # fused expert block
 # ------------------------------------------------------------------------------------------------
-# Fuse the expert-order gather into the A-operand load of the first expert GEMM.
-GATHER_IN_GEMM = os.environ.get("PITHTRAIN_GATHER_IN_GEMM", "0") == "1"
+# Fuse the expert-order gather into the A-operand load of the first expert GEMM (TMA tile::gather4 in the producer
+# warp). Correct (tests/test_gemm_gpu.py) but measured slower end to end than a separate gather pass, so off.
+GATHER_IN_GEMM = False
 
 
 class ExpertWeights:

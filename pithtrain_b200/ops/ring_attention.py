@@ -37,74 +37,39 @@ def _expand_kv(k: torch.Tensor, Hq: int) -> torch.Tensor:
     return k if Hkv == Hq else k.repeat_interleave(Hq // Hkv, dim=2)
 
 
-def block_mask(q_pos: torch.Tensor, k_pos: torch.Tensor, window_left: Optional[int]) -> torch.Tensor:
-    """Boolean ``[Sq, Sk]``: key visible to query (causal, optional sliding window)."""
-    m = k_pos.unsqueeze(0) <= q_pos.unsqueeze(1)
+def geometric_mask(Sq: int, Sk: int, causal: bool, q_off: int, window_left: Optional[int], device) -> Optional[torch.Tensor]:
+    """Boolean ``[Sq, Sk]`` of a block pair whose query row ``r`` sits at position ``q_off + r`` relative to key 0:
+    causal and sliding-window visibility; None when every key is visible."""
+    if not causal and window_left is None:
+        return None
+    qp = torch.arange(Sq, device=device).unsqueeze(1) + q_off
+    kp = torch.arange(Sk, device=device).unsqueeze(0)
+    m = torch.ones(Sq, Sk, dtype=torch.bool, device=device)
+    if causal:
+        m &= kp <= qp
     if window_left is not None:
-        m &= k_pos.unsqueeze(0) >= (q_pos.unsqueeze(1) - window_left)
+        m &= kp >= qp - window_left
     return m
 
 
-# Blocks that need no explicit mask (fully visible, or the causal diagonal block) go to the library (cuDNN) flash
-# kernel on GPUs, which returns the log-sum-exp the merge needs; everything else uses the fp32 math below.
-USE_LIBRARY_BLOCKS = True
-_LIB_BLOCKS_BROKEN = False
+def _own_kernels(q, k, v) -> bool:
+    from . import attention_native as N
+
+    return N.supported(q, k, v, True, None, None, None)
 
 
-def _lib_block_ok(q, k, v) -> bool:
-    return (USE_LIBRARY_BLOCKS and not _LIB_BLOCKS_BROKEN and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)
-            and q.shape[-1] == v.shape[-1] and q.shape[-1] % 8 == 0 and q.shape[-1] <= 256)
+def block_fwd(q, k, v, scale: float, causal: bool = False, q_off: int = 0, window_left: Optional[int] = None
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Partial attention of ``q[B,Sq,Hq,D]`` against ``k,v[B,Sk,Hkv,*]``: ``out[B,Sq,Hq,Dv]`` and fp32
+    ``lse[B,Hq,Sq]`` (``-inf`` for rows that see no key). Query row ``r`` sits at position ``q_off + r`` relative to
+    key 0; ``causal`` and ``window_left`` restrict visibility from there. bf16 blocks on a GPU run on the tcgen05
+    forward kernel (csrc/attention.cu), everything else on the fp32 math below."""
+    if _own_kernels(q, k, v):
+        from . import attention_native as N
 
-
-def _to_bhsd(t: torch.Tensor, Hq: int) -> torch.Tensor:
-    return _expand_kv(t, Hq).permute(0, 2, 1, 3)
-
-
-_LIB_BLOCKS_ERROR = ""
-
-
-def _lib_block_fwd(q, k, v, scale: float, causal: bool):
-    """cuDNN flash forward of one block; returns fp32 ``out[B,S,H,D]`` and ``lse[B,H,S]``."""
-    Hq = q.shape[2]
-    res = torch.ops.aten._scaled_dot_product_cudnn_attention(_to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq), None, True,
-                                                             0.0, causal, False, scale=scale)
-    out, lse = res[0], res[1]
-    B, H, S = out.shape[0], out.shape[1], out.shape[2]
-    return out.permute(0, 2, 1, 3).float(), lse.reshape(B, H, S).float()
-
-
-def _lib_block_bwd(do, q, k, v, out, lse, scale: float, causal: bool):
-    """cuDNN flash backward of one block against the *global* ``out``/``lse``."""
-    Hq, Hkv = q.shape[2], k.shape[2]
-    B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
-    dev = q.device
-    seed = torch.zeros((), dtype=torch.int64, device=dev)
-    qb, kb, vb = _to_bhsd(q, Hq), _to_bhsd(k, Hq), _to_bhsd(v, Hq)
-    ob = _to_bhsd(out.to(q.dtype), Hq)
-    dob = _to_bhsd(do.to(q.dtype), Hq)
-    lse4 = lse.float().reshape(B, Hq, Sq, 1).contiguous()
-    # undefined (None) cumulative-length tensors select the dense, non-nested path of the op
-    dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
-        dob, qb, kb, vb, ob, lse4, seed, seed, None, None, None, Sq, Sk, 0.0, causal, scale=scale)
-    dq, dk, dv = dq.permute(0, 2, 1, 3).float(), dk.permute(0, 2, 1, 3).float(), dv.permute(0, 2, 1, 3).float()
-    g = Hq // Hkv
-    if g > 1:
-        dk = dk.reshape(B, Sk, Hkv, g, -1).sum(3)
-        dv = dv.reshape(B, Sk, Hkv, g, -1).sum(3)
-    return dq, dk, dv
-
-
-def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor], causal_diag: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Partial attention of ``q[B,Sq,Hq,D]`` against ``k,v[B,Sk,Hkv,*]``: fp32 ``out[B,Sq,Hq,Dv]`` and
-    ``lse[B,Hq,Sq]`` (``-inf`` for rows that see no key). ``causal_diag`` says that ``mask`` is exactly the
-    causal mask of equal positions (the diagonal block without a sliding window)."""
-    global _LIB_BLOCKS_BROKEN
-    if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
-        try:
-            return _lib_block_fwd(q, k, v, scale, causal_diag)
-        except (RuntimeError, NotImplementedError, TypeError) as e:
-            global _LIB_BLOCKS_ERROR
-            _LIB_BLOCKS_BROKEN, _LIB_BLOCKS_ERROR = True, repr(e)  # no usable library kernel: keep to the math path
+        row_lo = N.row_lower_bounds(q.shape[0], q.shape[1], q_off, window_left, None, q.device)
+        return N.forward(q, k, v, scale, causal, q_off, row_lo, None)
+    mask = geometric_mask(q.shape[1], k.shape[1], causal, q_off, window_left, q.device)
     Hq = q.shape[2]
     qf = q.float().permute(0, 2, 1, 3)
     kf = _expand_kv(k, Hq).float().permute(0, 2, 1, 3)
@@ -119,15 +84,16 @@ def block_fwd(q, k, v, scale: float, mask: Optional[torch.Tensor], causal_diag: 
     return out, lse
 
 
-def block_bwd(do, q, k, v, out, lse, scale: float, mask: Optional[torch.Tensor], causal_diag: bool = False):
-    """Gradients of one partial given the *global* ``out``/``lse`` (flash-attention backward math)."""
-    global _LIB_BLOCKS_BROKEN
-    if (mask is None or causal_diag) and _lib_block_ok(q, k, v):
-        try:
-            return _lib_block_bwd(do, q, k, v, out, lse, scale, causal_diag)
-        except (RuntimeError, NotImplementedError, TypeError) as e:
-            global _LIB_BLOCKS_ERROR
-            _LIB_BLOCKS_BROKEN, _LIB_BLOCKS_ERROR = True, repr(e)
+def block_bwd(do, q, k, v, out, lse, scale: float, causal: bool = False, q_off: int = 0, window_left: Optional[int] = None):
+    """Gradients of one partial given the *global* ``out``/``lse`` (flash-attention backward math); the tcgen05
+    backward kernel (csrc/attention_bwd.cu) for the head dims it covers."""
+    from . import attention_native as N
+
+    if _own_kernels(q, k, v) and (q.shape[-1], v.shape[-1]) in N._BWD_DIMS and q.shape[1] % 4 == 0:
+        row_lo = N.row_lower_bounds(q.shape[0], q.shape[1], q_off, window_left, None, q.device)
+        dq, dk, dv, _ = N.backward(do.to(q.dtype), q, k, v, out.to(q.dtype), lse, scale, causal, q_off, row_lo)
+        return dq, dk, dv
+    mask = geometric_mask(q.shape[1], k.shape[1], causal, q_off, window_left, q.device)
     Hq, Hkv = q.shape[2], k.shape[2]
     g = Hq // Hkv
     qf = q.float().permute(0, 2, 1, 3)
@@ -154,6 +120,7 @@ def block_bwd(do, q, k, v, out, lse, scale: float, mask: Optional[torch.Tensor],
 
 def merge_partial(out: Optional[torch.Tensor], lse: Optional[torch.Tensor], o_p: torch.Tensor, lse_p: torch.Tensor):
     """Fold a partial ``(o_p, lse_p)`` into the running ``(out, lse)`` (all fp32)."""
+    o_p = o_p.float()
     if out is None:
         return o_p, lse_p
     new = torch.logaddexp(lse, lse_p)
@@ -180,10 +147,6 @@ def pair_relation(qb: int, kb: int, block: int, window_left: Optional[int]) -> s
             return "skip"
         return "mask"
     return "mask" if kb == qb else "full"
-
-
-def _positions(blk: int, block: int, device) -> torch.Tensor:
-    return torch.arange(blk * block, (blk + 1) * block, device=device)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -272,18 +235,20 @@ def _peer_pull_usable(group, cp: int, device) -> bool:
     return _PULL_OK[key]
 
 
-def _in_place_blocks_usable(q: torch.Tensor, payload, expand, window_left: Optional[int]) -> bool:
-    """Remote K/V blocks can be consumed where their owner published them when the own attention kernel is enabled in
-    its ring mode and the case is the one it covers: plain K and V (no latent to expand), no window, one sequence per
-    micro-batch, head dim 128, bf16, blocks that are multiples of 128 tokens."""
-    from . import attention_native as N
+# Forward steps read a peer's published K/V where it lies (the attention kernel's TMA loads cross NVLink) instead of
+# copying the block first.
+IN_PLACE_REMOTE_BLOCKS = True
 
-    if not N.RING_DIRECT or expand is not None or window_left is not None or len(payload) != 2:
+
+def _in_place_blocks_usable(q: torch.Tensor, payload, expand, window_left: Optional[int]) -> bool:
+    """Remote K/V blocks can be consumed where their owner published them in the case the kernel's pointer form covers:
+    plain K and V (no latent to expand), no window, one sequence per micro-batch, head dim 64 or 128, bf16."""
+    if not IN_PLACE_REMOTE_BLOCKS or expand is not None or window_left is not None or len(payload) != 2:
         return False
     k, v = payload
     B, S2, Hq, D = q.shape
-    return (B == 1 and D == 128 and k.shape[-1] == 128 and v.shape[-1] == 128 and q.dtype == torch.bfloat16
-            and k.dtype == torch.bfloat16 and (S2 // 2) % 128 == 0 and Hq % k.shape[2] == 0 and N._token_major(q[:, : S2 // 2]))
+    return (B == 1 and D in (64, 128) and k.shape[-1] == D and v.shape[-1] == D and q.dtype == torch.bfloat16
+            and k.dtype == torch.bfloat16 and Hq % k.shape[2] == 0)
 
 
 def _pairs(cp: int, rank: int, src: int, block: int, window_left: Optional[int]):
@@ -332,9 +297,8 @@ class _RingAttention(torch.autograd.Function):
                 k, v = expand(cur, params) if expand is not None else (cur[0], cur[1])
                 k_halves, v_halves = (k[:, :block], k[:, block:]), (v[:, :block], v[:, block:])
                 for qi, ki, rel, qb, kb in _pairs(cp, rank, src, block, window_left):
-                    mask = None if rel == "full" else block_mask(_positions(qb, block, dev), _positions(kb, block, dev), window_left)
-                    o_p, lse_p = block_fwd(q_halves[qi], k_halves[ki], v_halves[ki], scale, mask,
-                                           causal_diag=(rel == "mask" and window_left is None and qb == kb))
+                    o_p, lse_p = block_fwd(q_halves[qi], k_halves[ki], v_halves[ki], scale, rel == "mask",
+                                           (qb - kb) * block, window_left)
                     outs[qi], lses[qi] = merge_partial(outs[qi], lses[qi], o_p, lse_p)
             ring.end_step(i)
         ring.finish()
@@ -383,9 +347,8 @@ class _RingAttention(torch.autograd.Function):
                 k_h, v_h = halves(k.detach()), halves(v.detach())
                 dk_h, dv_h = halves(dk), halves(dv)
                 for qi, ki, rel, qb, kb in _pairs(cp, rank, src, block, window_left):
-                    mask = None if rel == "full" else block_mask(_positions(qb, block, dev), _positions(kb, block, dev), window_left)
-                    dq_p, dk_p, dv_p = block_bwd(do_h[qi], q_h[qi], k_h[ki], v_h[ki], out_h[qi], lse_h[qi], scale, mask,
-                                                 causal_diag=(rel == "mask" and window_left is None and qb == kb))
+                    dq_p, dk_p, dv_p = block_bwd(do_h[qi], q_h[qi], k_h[ki], v_h[ki], out_h[qi], lse_h[qi], scale,
+                                                 rel == "mask", (qb - kb) * block, window_left)
                     dq[qi] += dq_p
                     dk_h[ki].add_(dk_p)
                     dv_h[ki].add_(dv_p)

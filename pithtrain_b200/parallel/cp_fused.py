@@ -194,7 +194,9 @@ def usable(group, cp: int, device) -> bool:
     dev = torch.device(device)
     if dev.type != "cuda" or cp <= 1 or cp > 32:
         return False
-    ok = os.environ.get("PITHTRAIN_CP_BACKEND", "auto") != "nccl"
+    from ..contexts import distributed as dctx
+
+    ok = dctx.cp_backend != "nccl"
     local_world = max(int(os.environ.get("LOCAL_WORLD_SIZE", "1")), 1)
     ranks = dist.get_process_group_ranks(group) if group is not None else list(range(dist.get_world_size()))
     me = dist.get_rank()

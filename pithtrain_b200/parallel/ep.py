@@ -200,7 +200,7 @@ def _fused_transport_usable(d) -> bool:
     return bool(flag.item())
 
 
-def setup_exchange(backend: str = "auto"):
+def setup_exchange(backend: str = "auto", capacity_factor: float | None = None):
     """Create the process-wide exchange from the distributed context (call after setup_distributed)."""
     from ..contexts import distributed
 
@@ -212,7 +212,7 @@ def setup_exchange(backend: str = "auto"):
     if backend == "fused":
         from .ep_fused import FusedExchange
 
-        ex = FusedExchange(distributed.ep_group, distributed.ep_size, distributed.ep_rank)
+        ex = FusedExchange(distributed.ep_group, distributed.ep_size, distributed.ep_rank, capacity_factor)
     else:
         ex = CollectiveExchange(distributed.ep_group, distributed.ep_size, distributed.ep_rank)
     set_current(ex)

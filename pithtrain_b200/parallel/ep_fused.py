@@ -12,9 +12,10 @@ Same contract as :class:`pithtrain_b200.parallel.ep.CollectiveExchange`, but
 * backward of each direction is the other direction over the same plan.
 
 Four channels (dispatch/combine × forward/backward), two slots each, sized once from the first
-micro-batch shape. Receive capacity is ``capacity_factor`` times the expected de-duplicated volume
-(never less than the exact worst case when that is small); overflow is reported through the
-library's status word instead of corrupting memory.
+micro-batch shape. Receive capacity is the exact worst case (every token of every rank routed here,
+``ep * m`` rows) unless ``capacity_factor`` is given explicitly, in which case it is that multiple of the
+expected de-duplicated volume: an opt-in that saves memory for well-balanced routers. An overflow of a reduced
+capacity sets the status word, which the train step reads once per step and turns into an error on every rank.
 """
 
 from __future__ import annotations
@@ -168,7 +169,7 @@ class _FusedCombine(torch.autograd.Function):
 
 
 class FusedExchange(Exchange):
-    def __init__(self, group, ep_size: int, ep_rank: int, capacity_factor: float = 1.5) -> None:
+    def __init__(self, group, ep_size: int, ep_rank: int, capacity_factor: float | None = None) -> None:
         assert ep_size <= EP_MAX
         self.group, self.ep, self.rank = group, ep_size, ep_rank
         self.capacity_factor = capacity_factor
@@ -182,9 +183,11 @@ class FusedExchange(Exchange):
             return
         self.cap = m
         worst = self.ep * m
-        expected = self.ep * m * (1.0 - ((self.ep - 1) / self.ep) ** k)
-        want = int(self.capacity_factor * expected) + m
-        self.cap_total = worst if worst * H * elem_size <= (64 << 20) else min(worst, (want + 127) // 128 * 128)
+        self.cap_total = worst
+        if self.capacity_factor is not None:
+            expected = self.ep * m * (1.0 - ((self.ep - 1) / self.ep) ** k)
+            want = int(self.capacity_factor * expected) + m
+            self.cap_total = min(worst, (want + 127) // 128 * 128)
         W = H * elem_size
         for name, kk in (("dispatch_f", k), ("dispatch_b", k), ("combine_f", 0), ("combine_b", 0)):
             self.channels[name] = Channel(self.group, self.ep, self.rank, m, W, kk, device)

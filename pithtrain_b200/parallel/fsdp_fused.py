@@ -103,7 +103,9 @@ def usable(group, group_size: int, device) -> bool:
     dev = torch.device(device)
     if dev.type != "cuda" or group_size <= 1 or group_size > MAXW:
         return False
-    ok = os.environ.get("PITHTRAIN_FSDP_BACKEND", "auto") != "nccl"
+    from ..contexts import distributed as dctx
+
+    ok = dctx.shard_backend != "nccl"
     local_world = int(os.environ.get("LOCAL_WORLD_SIZE", "1"))
     ranks = dist.get_process_group_ranks(group)
     me_global = dist.get_rank()

@@ -197,6 +197,27 @@ def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], 
     return loss, gradient_norm
 
 
+def read_kernel_status() -> int:
+    """The device status word (4-byte device-to-host copy, cleared on read): non-zero when a bounded in-kernel wait ran
+    out or a receive buffer overflowed during the step. 0 without the native library."""
+    from .. import _native
+
+    return _native.fetch_status() if _native.available() else 0
+
+
+def raise_on_kernel_status(worst: int, own: int) -> None:
+    """Raise on every rank when any rank's kernels reported a problem in this step: a transport whose wait timed out
+    skipped its reduction or consumed stale rows, so the step's result must not be kept (nor checkpointed)."""
+    if worst > 0:
+        from .. import _native
+
+        name = _native.STATUS_NAMES.get(worst, f"status {worst}")
+        mine = _native.STATUS_NAMES.get(own, "none") if own else "none"
+        raise _native.KernelStatusError(
+            f"step {training.step}: a kernel reported '{name}' on at least one rank (this rank: {mine}); "
+            "the step's gradients are not trustworthy")
+
+
 def train_step(cfg: PretrainLMCfg) -> dict:
     """One optimizer step. Returns the step's metrics (populated on every rank)."""
     t = cfg.training
@@ -222,14 +243,17 @@ def train_step(cfg: PretrainLMCfg) -> dict:
     schedulers = training.schedulers
 
     device_ms = None
+    status = 0
     if use_cuda:
         ev1.record()
         torch.cuda.synchronize()
         device_ms = ev0.elapsed_time(ev1)
-    dt = torch.tensor([time.time() - t0, (device_ms or 0.0) / 1e3], device=d.device)
+        status = read_kernel_status()
+    dt = torch.tensor([time.time() - t0, (device_ms or 0.0) / 1e3, float(status)], device=d.device)
     if dist.is_initialized() and d.world_size > 1:
         dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-    elapsed, device_s = dt.tolist()
+    elapsed, device_s, worst = dt.tolist()
+    raise_on_kernel_status(int(worst), status)
 
     peak = torch.tensor(torch.cuda.max_memory_allocated() / 1024 ** 3 if use_cuda else 0.0, device=d.device)
     if dist.is_initialized() and d.world_size > 1:

@@ -31,8 +31,10 @@ def token_counts(dims: ModelDims, par: ParallelCfg, imbalance: float = 1.0) -> T
     pairs = int(T * k * imbalance)
     worst = ep * T
     if par.ep_backend == "fused" and ep > 1:
-        want = int(par.capacity_factor * ep * T * hit) + T
-        cap = worst if worst * dims.H * 2 <= (64 << 20) else min(worst, (want + 127) // 128 * 128)
+        cap = worst  # exact worst case unless a capacity factor is opted into
+        if par.capacity_factor is not None:
+            want = int(par.capacity_factor * ep * T * hit) + T
+            cap = min(worst, (want + 127) // 128 * 128)
     else:
         cap = recv
     return TokenCounts(T=T, recv=min(recv, worst), sorted_rows=pairs + 16 * (dims.E // ep), recv_capacity=cap)

@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 from ...dualpipe.dualpipev import layer_partition
 
@@ -36,7 +36,7 @@ class ParallelCfg:
     resident_state_gb: float = 0.0  # with offload: GiB of optimizer state kept on the device anyway
     ep_backend: str = "fused"  # "fused" (symmetric buffers) or "nccl"
     fp8_training: bool = False  # block-scaled e4m3 forward / input-gradient GEMMs: cached quantised weight copies
-    capacity_factor: float = 1.5
+    capacity_factor: Optional[float] = None
 
     @property
     def world(self) -> int:

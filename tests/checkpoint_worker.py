@@ -81,3 +81,31 @@ def run(rank, world, pp, ep, save_location, phase, model="qwen3"):
                     assert torch.allclose(v.float().cpu(), expect_o[k][f].float().cpu()), f"optimizer mismatch {k}.{f}"
         assert abs(training.schedulers[0].get_last_lr()[0] - 1e-2) < 1e-9
         train_step(cfg)  # resumed run keeps training
+
+
+def run_strict(rank, world, save_location):
+    """A checkpoint with one expert tensor missing: the default load refuses it, ``strict=False`` loads the rest."""
+    import torch.distributed.checkpoint as dcp
+
+    from pithtrain_b200.contexts import training
+    from pithtrain_b200.modules.checkpoint import build_save_state, load_into
+    from pithtrain_b200.modules.distributed import setup_distributed
+    from pithtrain_b200.modules.logging import setup_logging
+    from pithtrain_b200.modules.training import setup_training
+
+    cfg = make_cfg(1, 1, save_location, 4)
+    setup_logging(cfg)
+    setup_distributed(cfg, failfast=False)
+    setup_training(cfg)
+    state = build_save_state(training.model, training.optimizers, training.schedulers)
+    victim = next(k for k in state["app"]["model"] if ".experts.3." in k)
+    del state["app"]["model"][victim]
+    path = Path(save_location, "damaged")
+    dcp.save(state, checkpoint_id=str(path))
+    try:
+        load_into(path, training.model, training.optimizers, training.schedulers)
+    except KeyError as e:
+        assert victim in str(e), str(e)
+    else:
+        raise AssertionError("a checkpoint lacking a model tensor loaded without an error")
+    load_into(path, training.model, training.optimizers, training.schedulers, strict=False)

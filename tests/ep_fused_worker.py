@@ -24,7 +24,11 @@ def run(rank: int, world: int, m: int, H: int, E: int, k: int, rounds: int = 3):
     for it in range(rounds):
         x0 = torch.randn(m, H, generator=g).to(dev).bfloat16()
         w0 = torch.rand(m, k, generator=g).to(dev)
-        idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(m)]).int().to(dev)
+        if it == rounds - 1 and E // world >= k:
+            # collapsed router: every token of every rank goes to rank 0's experts (the exact worst case, ep * m rows)
+            idx = torch.stack([torch.randperm(E // world, generator=g)[:k] for _ in range(m)]).int().to(dev)
+        else:
+            idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(m)]).int().to(dev)
         outs = []
         for ex in (base, fused):
             x, w = x0.clone().requires_grad_(), w0.clone().requires_grad_()

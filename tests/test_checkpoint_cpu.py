@@ -114,6 +114,10 @@ def test_interrupted_save_is_skipped_on_resume(tmp_path):
         launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")
 
 
+def test_load_refuses_a_checkpoint_that_lacks_model_tensors(tmp_path):
+    launch(1, checkpoint_worker.run_strict, str(tmp_path), timeout=300.0)
+
+
 def test_app_state_roundtrip_in_one_process():
     import train_worker
 

@@ -219,33 +219,33 @@ def test_route_sort_device_side_count(n, k, E, valid):
     assert torch.equal(sor.cpu(), sor_r)
 
 
-@pytest.mark.parametrize("causal", [False, True])
-def test_ring_blocks_library_vs_math(causal):
-    """The flash-kernel block path of ring attention (with a *global* lse in the backward) equals the fp32 math."""
+@pytest.mark.parametrize("causal,q_off,window", [(False, 0, None), (True, 0, None), (True, 256, 300), (True, 0, 100)])
+def test_ring_blocks_kernel_vs_math(causal, q_off, window):
+    """The kernel block path of ring attention (with a *global* lse in the backward) equals the fp32 math."""
+    from pithtrain_b200.ops import attention_native as N
     from pithtrain_b200.ops import ring_attention as R
 
     torch.manual_seed(11)
     B, S, Hq, Hkv, D = 2, 256, 8, 2, 64
     q, k, v = bf(B, S, Hq, D), bf(B, S, Hkv, D), bf(B, S, Hkv, D)
     do = bf(B, S, Hq, D)
-    pos = torch.arange(S, device="cuda")
-    mask = R.block_mask(pos, pos, None) if causal else None
     outs = []
-    for lib in (True, False):
-        R.USE_LIBRARY_BLOCKS = lib
+    for own in (True, False):
+        N.ENABLED = own
         try:
-            o, lse = R.block_fwd(q, k, v, D ** -0.5, mask, causal_diag=causal)
+            o, lse = R.block_fwd(q, k, v, D ** -0.5, causal, q_off, window)
             # a larger global lse, as when other blocks contributed too
             lse_g = lse + 0.3
-            o_g = o * torch.exp(lse - lse_g).permute(0, 2, 1).unsqueeze(-1)
-            grads = R.block_bwd(do, q, k, v, o_g, lse_g, D ** -0.5, mask, causal_diag=causal)
+            o_g = o.float() * torch.exp(lse - lse_g).permute(0, 2, 1).unsqueeze(-1)
+            grads = R.block_bwd(do, q, k, v, o_g, lse_g, D ** -0.5, causal, q_off, window)
             outs.append((o, lse) + tuple(grads))
         finally:
-            R.USE_LIBRARY_BLOCKS = True
-    assert not R._LIB_BLOCKS_BROKEN, "the library flash kernel was not usable on this device: " + R._LIB_BLOCKS_ERROR
+            N.ENABLED = True
+    _native.check_status()
     for a, b in zip(*outs):
         assert a.shape == b.shape
-        assert calc_diff(a.float(), b.float()) < 2e-4
+        fin = torch.isfinite(b.float())
+        assert calc_diff(a.float()[fin], b.float()[fin]) < 3e-4
 
 
 def test_bounded_wait_reports_through_status_word():
@@ -255,17 +255,40 @@ def test_bounded_wait_reports_through_status_word():
 
     ctl = torch.zeros(128, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
-    t0 = time.time()
-    rc = _native.lib().pt_symm_wait(ctl.data_ptr(), 0, 1, 1, _native.stream_ptr())
-    assert rc == 0
-    torch.cuda.synchronize()
-    waited = time.time() - t0
-    assert 1.0 < waited < 10.0, waited  # the limit is 2 s
-    with pytest.raises(RuntimeError, match="4|peer|timeout"):
-        _native.check_status()
-    _native.check_status()  # cleared by the read
-    y = bf(64, 64) + 1  # the context still works
-    assert torch.isfinite(y.float()).all()
+    _native.set_peer_wait_limit(0.5)  # the run-time limit of waits on a peer's flag
+    try:
+        t0 = time.time()
+        rc = _native.lib().pt_symm_wait(ctl.data_ptr(), 0, 1, 1, _native.stream_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        waited = time.time() - t0
+        assert 0.3 < waited < 5.0, waited
+        with pytest.raises(RuntimeError, match="4|peer|timeout"):
+            _native.check_status()
+        _native.check_status()  # cleared by the read
+        y = bf(64, 64) + 1  # the context still works
+        assert torch.isfinite(y.float()).all()
+    finally:
+        _native.set_peer_wait_limit(2.0)
+
+
+def test_train_step_status_check_raises_after_a_timed_out_wait():
+    """What the train step does once per step: read the status word and raise on every rank if a wait ran out."""
+    from pithtrain_b200.tasks.pretrain_lm import raise_on_kernel_status, read_kernel_status
+
+    ctl = torch.zeros(128, dtype=torch.int32, device="cuda")
+    _native.set_peer_wait_limit(0.2)
+    try:
+        assert _native.lib().pt_symm_wait(ctl.data_ptr(), 0, 1, 1, _native.stream_ptr()) == 0
+        torch.cuda.synchronize()
+        status = read_kernel_status()
+        assert status == 4
+        with pytest.raises(_native.KernelStatusError, match="peer"):
+            raise_on_kernel_status(status, status)
+        assert read_kernel_status() == 0  # cleared by the read
+        raise_on_kernel_status(0, 0)      # a clean step passes
+    finally:
+        _native.set_peer_wait_limit(2.0)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -286,7 +309,7 @@ def test_accumulate_colsum_into_main_grad(dtype):
 
 
 def test_attention_sinks_and_packed_paths_on_gpu():
-    """Sinks through the library flash kernel (rescaled log-sum-exp) and packed sequences document by document."""
+    """Sinks, packed sequences and sliding windows through the public entry point."""
     from pithtrain_b200.ops import attention as A
 
     torch.manual_seed(13)
@@ -298,11 +321,8 @@ def test_attention_sinks_and_packed_paths_on_gpu():
     got = (out,) + torch.autograd.grad(out, [q, k, v, sinks], go)
     ref = A.attention_ref(q, k, v, True, None, None, sinks, None)
     want = (ref,) + torch.autograd.grad(ref, [q, k, v, sinks], go)
-    from pithtrain_b200.ops import ring_attention as R
-
-    assert not R._LIB_BLOCKS_BROKEN, R._LIB_BLOCKS_ERROR
     for a, b in zip(got, want):
-        assert calc_diff(a.float(), b.float()) < 3e-4
+        assert calc_diff(a.float(), b.float()) < 5e-4
     cu = torch.tensor([0, 100, 300, S], dtype=torch.int32, device="cuda")
     out = A.attention(q, k, v, True, None, None, None, cu)
     ref = A.attention_ref(q, k, v, True, None, None, None, cu)
@@ -310,27 +330,6 @@ def test_attention_sinks_and_packed_paths_on_gpu():
     out = A.attention(q, k, v, True, None, 127, sinks, None)  # GPT-OSS sliding-window layer: blocked form
     ref = A.attention_ref(q, k, v, True, None, 127, sinks, None)
     assert calc_diff(out.float(), ref.float()) < 3e-4
-
-
-@pytest.mark.skipif(os.environ.get("PITHTRAIN_OWN_ATTENTION", "0") != "1",
-                    reason="the tcgen05 attention forward runs only with PITHTRAIN_OWN_ATTENTION=1 until it is validated")
-@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 4, 2), (2, 1024, 8, 2), (1, 4096, 8, 1)])
-def test_own_causal_attention_forward(B, S, Hq, Hkv):
-    from pithtrain_b200.ops import attention_native as N
-    from pithtrain_b200.ops.attention import attention_ref
-
-    torch.manual_seed(11)
-    qkv = bf(B, S, (Hq + 2 * Hkv) * 128, scale=1.0)  # slices of one projection output, like the model's
-    q = qkv[..., :Hq * 128].view(B, S, Hq, 128).requires_grad_()
-    k = qkv[..., Hq * 128:(Hq + Hkv) * 128].view(B, S, Hkv, 128)
-    v = qkv[..., (Hq + Hkv) * 128:].view(B, S, Hkv, 128)
-    assert N.causal_d128_supported(q, k, v, True, None, None, None)
-    out, lse = N.causal_d128_attention(q, k, v, True, None, None, None, None, return_lse=True)
-    torch.cuda.synchronize()
-    _native.check_status()
-    ref, ref_lse = attention_ref(q, k, v, causal=True, return_lse=True)
-    assert calc_diff(out.float(), ref.float()) < 1e-3
-    assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)
 
 
 @pytest.mark.skipif(os.environ.get("PITHTRAIN_NS_GEMM", "library") != "own",

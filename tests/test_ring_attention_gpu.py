@@ -17,9 +17,9 @@ def test_ring_attention_peer_pull(case):
     launch(n, ring_worker.run, case, "cuda", 4, backend="nccl")
 
 
-@pytest.mark.skipif(__import__("os").environ.get("PITHTRAIN_OWN_ATTENTION", "0") != "ring",
-                    reason="the in-place ring mode of the tcgen05 attention kernel runs only with PITHTRAIN_OWN_ATTENTION=ring")
 def test_ring_attention_reads_peer_blocks_in_place():
+    """bf16, head dim 128, no window: forward steps hand the attention kernel the address of the peer's published K/V
+    (ops/ring_attention.py: IN_PLACE_REMOTE_BLOCKS), so its TMA loads fetch the block over NVLink while it computes."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     launch(2, ring_worker.run, "gqa_d128_bf16", "cuda", 3, backend="nccl")

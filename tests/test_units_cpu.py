@@ -318,39 +318,23 @@ def test_blocked_sliding_window_attention(window, use_sinks, packed):
         assert torch.allclose(attention(q, k, v, True, None, window, sinks, cu), ref, atol=2e-5, rtol=1e-4)
 
 
-def test_attention_per_document_equals_masked_attention():
-    from pithtrain_b200.ops.attention import attention_per_document, attention_ref
-
-    torch.manual_seed(1)
-    q, k, v = torch.randn(1, 96, 4, 8), torch.randn(1, 96, 2, 8), torch.randn(1, 96, 2, 8)
-    cu = torch.tensor([0, 17, 64, 96], dtype=torch.int32)
-    sinks = torch.randn(4)
-    got = attention_per_document(q, k, v, cu, None, sinks, inner=attention_ref)
-    assert torch.allclose(got, attention_ref(q, k, v, True, None, None, sinks, cu), atol=1e-5)
-
-
-def test_own_attention_is_opt_in_and_shape_gated():
-    """The tcgen05 attention forward is registered only by an explicit switch, and its predicate accepts exactly the
-    layouts the kernel's tensor maps can describe."""
-    import os
-
+def test_own_attention_predicate_and_row_bounds():
+    """The kernels' predicate refuses CPU tensors, fp32 and head dims outside their set; the per-row lower key bounds
+    fold sliding windows and document starts into one vector."""
     from pithtrain_b200.ops import attention_native as N
 
-    if os.environ.get("PITHTRAIN_OWN_ATTENTION", "0") != "1":
-        assert N._IMPL is None
-    qkv = torch.zeros(2, 256, (8 + 2 * 2) * 128, dtype=torch.bfloat16)
-    q = qkv[..., :1024].view(2, 256, 8, 128)
-    k = qkv[..., 1024:1280].view(2, 256, 2, 128)
-    v = qkv[..., 1280:].view(2, 256, 2, 128)
-    ok = N.causal_d128_supported
-    assert ok(q, k, v, True, None, None, None)
-    assert not ok(q, k, v, False, None, None, None) and not ok(q, k, v, True, 127, None, None)
-    assert not ok(q, k, v, True, None, torch.zeros(8), None) and not ok(q, k, v, True, None, None, torch.tensor([0, 256]))
-    assert not ok(q.float(), k, v, True, None, None, None)
-    assert not ok(q[:, :200], k[:, :200], v[:, :200], True, None, None, None)  # not a multiple of 128
-    assert not ok(q.transpose(1, 2).contiguous().transpose(1, 2), k, v, True, None, None, None)  # head-major storage
-    assert not ok(q[..., :64], k[..., :64], v[..., :64], True, None, None, None)
-    assert not N.supported(q, k, v, True, None, None, None)  # CPU tensors never take the kernel
+    q = torch.zeros(2, 256, 8, 128, dtype=torch.bfloat16)
+    k = v = torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16)
+    assert not N.supported(q, k, v, True, None, None, None)  # CPU tensors never take the kernels
+    assert N.row_lower_bounds(2, 256, 0, None, None, "cpu") is None
+    lo = N.row_lower_bounds(1, 8, 0, 2, None, "cpu")
+    assert lo.tolist() == [0, 0, 0, 1, 2, 3, 4, 5]
+    lo = N.row_lower_bounds(1, 8, 4, 2, None, "cpu")  # queries 4 positions ahead of key 0
+    assert lo.tolist() == [2, 3, 4, 5, 6, 7, 8, 9]
+    cu = torch.tensor([0, 3, 8], dtype=torch.int32)
+    assert N.row_lower_bounds(1, 8, 0, None, cu, "cpu").tolist() == [0, 0, 0, 3, 3, 3, 3, 3]
+    assert N.row_lower_bounds(1, 8, 0, 1, cu, "cpu").tolist() == [0, 0, 1, 3, 3, 4, 5, 6]
+    assert N.row_lower_bounds(2, 4, 0, 1, None, "cpu").tolist() == [0, 0, 1, 2, 0, 0, 1, 2]
 
 
 @pytest.mark.parametrize("shape", [(3, 64, 128), (2, 128, 64), (64, 64), (1, 192, 64)])
@@ -456,14 +440,21 @@ def test_new_entry_points_validate_their_arguments_on_the_host():
     if torch.cuda.is_available():
         pytest.skip("host-only check")
     L = ctypes.CDLL(str(lib))
-    for name in ("pt_attn_fwd_causal", "pt_attn_fwd_block", "pt_gemm2cta_nt"):
+    for name in ("pt_attn_fwd", "pt_attn_bwd", "pt_gemm2cta_nt"):
         fn = getattr(L, name)
         fn.argtypes = [_native._CT[a] for a in _native.SIGS[name]]
         fn.restype = ctypes.c_int
     N = None
-    assert L.pt_attn_fwd_causal(N, N, N, N, N, 1, 100, 4, 2, 512, 256, 256, 512, 0.1, N) == -2  # S not a multiple of 128
-    assert L.pt_attn_fwd_causal(N, N, N, N, N, 1, 256, 5, 2, 640, 256, 256, 640, 0.1, N) == -2  # heads not divisible
-    assert L.pt_attn_fwd_block(N, N, N, N, N, 1, 256, 0, 4, 2, 512, 256, 256, 512, 0.1, N) == -2  # no keys
-    assert L.pt_attn_fwd_block(N, N, N, N, N, 1, 256, 128, 4, 2, 512, 256, 256, 512, 0.1, N) == -3
+    fwd = lambda Sq, Sk, Hq, Hkv, dqk, dv: L.pt_attn_fwd(N, N, N, N, N, N, N, 1, Sq, Sk, Hq, Hkv, dqk, dv, Hq * dqk, Hkv * dqk,
+                                                         Hkv * dv, Hq * dv, 0.1, 1, 0, N)
+    assert fwd(256, 256, 5, 2, 128, 128) == -2  # heads not divisible
+    assert fwd(256, 0, 4, 2, 128, 128) == -2    # no keys
+    assert fwd(256, 256, 4, 2, 96, 96) == -2    # head dim outside the kernels' set
+    assert fwd(256, 128, 4, 2, 128, 128) == -3
+    bwd = lambda Sq, Hq, Hkv, dd: L.pt_attn_bwd(N, N, N, N, N, N, N, N, N, N, N, N, N, N, N, 1, Sq, Sq, Hq, Hkv, dd, Hq * dd,
+                                                Hkv * dd, Hkv * dd, Hq * dd, Hq * dd, 0.1, 1, 0, N)
+    assert bwd(256, 5, 2, 128) == -2
+    assert bwd(256, 4, 2, 192) == -2            # the backward covers head dims 64 and 128
+    assert bwd(256, 4, 2, 128) == -3
     assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 60, 60, 60, 256, N) == -2  # K not a multiple of 8
     assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 64, 64, 64, 256, N) == -3

@@ -77,3 +77,42 @@ def test_route_sort_noalloc_rejects_oversize():
     r_cap = 64 + 16 * E
     rc, offs, ros, sor = _noalloc(L, eids, E, 16, r_cap)
     assert rc == -2
+
+
+def test_route_sort_noalloc_accepts_the_maximum_expert_count():
+    from pithtrain_b200 import _native
+
+    L = _native.lib()
+    torch.manual_seed(12)
+    E, n, align = MAX_EXPERTS, 5000, 16
+    eids = torch.randint(-1, E, (n,), device="cuda", dtype=torch.int32)
+    r_cap = (n + align * E + 127) // 128 * 128
+    ref_offs, ref_ros, ref_sor = _regular(L, eids, E, align, r_cap)
+    rc, offs, ros, sor = _noalloc(L, eids, E, align, r_cap)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(offs, ref_offs) and torch.equal(ros, ref_ros) and torch.equal(sor, ref_sor)
+
+
+def test_route_sort_noalloc_writes_nothing_past_a_too_small_row_capacity():
+    """Rows that do not fit: ``offs[E] > r_cap`` reports it and the words behind ``slot_of_row[r_cap]`` stay untouched."""
+    from pithtrain_b200 import _native
+
+    L = _native.lib()
+    torch.manual_seed(13)
+    E, n, align, r_cap, guard = 8, 1024, 16, 512, 256
+    eids = torch.randint(0, E, (n,), device="cuda", dtype=torch.int32)
+    offs = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    ros = torch.empty(n, dtype=torch.int32, device="cuda")
+    sor = torch.full((r_cap + guard,), 0x5A5A5A5A, dtype=torch.int32, device="cuda")
+    fn = L.pt_route_sort_noalloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                   ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    rc = fn(eids.data_ptr(), n, E, align, offs.data_ptr(), ros.data_ptr(), sor.data_ptr(), r_cap,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(offs[E]) > r_cap
+    assert bool((sor[r_cap:] == 0x5A5A5A5A).all())
+    _native.fetch_status()  # the regular path records the overflow in the status word; leave it clean for later tests
