@@ -69,6 +69,8 @@ SIGS = {
     "pt_route_sort": "PPIIIPLPPPIP",
     "pt_route_sort_noalloc": "PIIIPPPIP",
     "pt_gather_rows": "PPIPPIILP",
+    "pt_indexed_bias_add": "PPPIPPIIP",
+    "pt_segment_sum": "PIPPIPIP",
     "pt_combine": "PPPPPPIIIP",
     "pt_swiglu_fwd": "PPPIIIFFP",
     "pt_swiglu_bwd": "PPPPPPPIIIFFPP",

@@ -433,6 +433,81 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __r
   }
 }
 
+
+// ----------------------------------------------------------------------------------------------
+// Per-expert biases on expert-sorted rows (GPT-OSS). Takes the role of the reference's
+// pithtrain/operators/indexed_bias_add.py (forward :54-83, segmented bias gradient :20-51).
+//   indexed_bias_add: out[r] = x[r] + bias[group(r)], group(r) found by binary search in offs; one warp per row.
+//   segment_sum:      out[g, c] = sum over rows of group g of x[r, c] * (row_w ? row_w[r] : 1), fp32, no atomics:
+//                     one CTA per (group, 256-column slab), rows walked in order (deterministic).
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ int group_of_row(const int* __restrict__ offs, int E, int r) {
+  int lo = 0, hi = E - 1;  // largest g with offs[g] <= r (rows past offs[E] map to the last group)
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (offs[mid] <= r) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(256)
+indexed_bias_add_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
+                        const int* __restrict__ offs, int E, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ n_rows_ptr, int n_rows_max, int H) {
+  const int n_rows = n_rows_ptr ? min(*n_rows_ptr, n_rows_max) : n_rows_max;
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * wpb) {
+    const int g = group_of_row(offs, E, r);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * H);
+    const uint4* br = reinterpret_cast<const uint4*>(bias + (size_t)g * H);
+    uint4* orow = reinterpret_cast<uint4*>(out + (size_t)r * H);
+    for (int c = lane; c < H / 8; c += 32) {
+      const uint4 a = xr[c], b = br[c];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 u = unpack_bf16x2(aw[i]), v = unpack_bf16x2(bw[i]);
+        o[i] = pack_bf16x2(u.x + v.x, u.y + v.y);
+      }
+      orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+segment_sum_kernel(const T* __restrict__ x, const float* __restrict__ row_w, const int* __restrict__ offs,
+                   float* __restrict__ out, int H) {
+  const int g = blockIdx.x;
+  const int c = (blockIdx.y * 128 + threadIdx.x) * 2;
+  if (c >= H) return;
+  const int r0 = offs[g], r1 = offs[g + 1];
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  int r = r0;
+  for (; r + 1 < r1; r += 2) {
+    float2 u, v;
+    if constexpr (sizeof(T) == 2) {
+      u = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (size_t)r * H + c));
+      v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (size_t)(r + 1) * H + c));
+    } else {
+      u = *reinterpret_cast<const float2*>(x + (size_t)r * H + c);
+      v = *reinterpret_cast<const float2*>(x + (size_t)(r + 1) * H + c);
+    }
+    const float wu = row_w ? row_w[r] : 1.f, wv = row_w ? row_w[r + 1] : 1.f;
+    a0 = fmaf(u.x, wu, a0); a1 = fmaf(u.y, wu, a1);
+    b0 = fmaf(v.x, wv, b0); b1 = fmaf(v.y, wv, b1);
+  }
+  if (r < r1) {
+    float2 u;
+    if constexpr (sizeof(T) == 2) u = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (size_t)r * H + c));
+    else u = *reinterpret_cast<const float2*>(x + (size_t)r * H + c);
+    const float wu = row_w ? row_w[r] : 1.f;
+    a0 = fmaf(u.x, wu, a0); a1 = fmaf(u.y, wu, a1);
+  }
+  *reinterpret_cast<float2*>(out + (size_t)g * H + c) = make_float2(a0 + b0, a1 + b1);
+}
+
 }  // namespace pt
 
 using namespace pt;
@@ -707,5 +782,30 @@ PT_API int pt_swiglu_bwd(const void* gu, const void* dact, const float* row_w, v
   swiglu_bwd_kernel<<<grid_for(n_rows_max, 8, 16), 256, 0, st>>>((const __nv_bfloat16*)gu,
       (const __nv_bfloat16*)dact, row_w, (__nv_bfloat16*)dgu, (__nv_bfloat16*)act_scaled, d_row_w,
       n_rows_ptr, n_rows_max, I, interleaved, alpha, limit, slot_of_row);
+  return (int)cudaGetLastError();
+}
+
+// out[r] = x[r] + bias[group(r)] for the first n rows (device-side count optional); x, bias, out bf16, H % 8 == 0;
+// out may alias x.
+PT_API int pt_indexed_bias_add(const void* x, const void* bias, const int* offs, int E, void* out, const int* n_rows_ptr,
+                               int n_rows_max, int H, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_rows_max <= 0) return 0;
+  if (H % 8 != 0 || E <= 0) return -1;
+  indexed_bias_add_kernel<<<grid_for(n_rows_max, 8, 16), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)bias,
+                                                                       offs, E, (__nv_bfloat16*)out, n_rows_ptr, n_rows_max, H);
+  return (int)cudaGetLastError();
+}
+
+// out[g, :] = sum of rows [offs[g], offs[g+1]) of x (bf16 when x_fp32 == 0, else fp32), optionally weighted per row;
+// out fp32 [E, H], H even.
+PT_API int pt_segment_sum(const void* x, int x_fp32, const float* row_w, const int* offs, int E, float* out, int H,
+                          void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (E <= 0 || H <= 0) return 0;
+  if (H % 2 != 0) return -1;
+  dim3 grid(E, (H / 2 + 127) / 128);
+  if (x_fp32) segment_sum_kernel<float><<<grid, 128, 0, st>>>((const float*)x, row_w, offs, out, H);
+  else segment_sum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, row_w, offs, out, H);
   return (int)cudaGetLastError();
 }

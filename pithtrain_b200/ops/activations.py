@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from .common import accumulate_grad
-from .moe import segment_sum, swiglu_bwd, swiglu_fwd
+from .moe import indexed_bias_add_rows, segment_sum, swiglu_bwd, swiglu_fwd
 
 
 class _SwiGLUFn(torch.autograd.Function):
@@ -47,13 +47,9 @@ def clamped_swiglu(gate_up: torch.Tensor, alpha: float = 1.702, limit: float = 7
 class _IndexedBiasAddFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, bias, offs):
-        R = x.shape[0]
-        E = bias.shape[0]
-        row = torch.arange(R, device=x.device)
-        gid = torch.bucketize(row, offs[1:].long(), right=True).clamp(max=E - 1)
         ctx.save_for_backward(offs)
         ctx.bias_ref = bias
-        return x + bias.detach()[gid].to(x.dtype)
+        return indexed_bias_add_rows(x, bias.detach(), offs)
 
     @staticmethod
     def backward(ctx, dy):

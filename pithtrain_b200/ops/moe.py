@@ -211,14 +211,40 @@ def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor, row_w: Optional[torch.Tenso
     return dguf.to(gu.dtype), act, dw
 
 
-def segment_sum(x: torch.Tensor, offs: torch.Tensor, num_groups: int) -> torch.Tensor:
-    """Per-group column sums ``[G, H]`` in fp32 of rows ``[offs[g], offs[g+1])`` (bias gradients)."""
-    # A segmented reduction over the sorted rows: one pass, no atomics, deterministic. (An ``index_add_`` by group id
+def segment_sum(x: torch.Tensor, offs: torch.Tensor, num_groups: int, row_w: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-group column sums ``[G, H]`` in fp32 of rows ``[offs[g], offs[g+1])`` (bias gradients), each row optionally
+    scaled by ``row_w[r]``."""
+    # A segmented reduction over the sorted rows: one pass, no atomics, deterministic: one CTA per (group, column slab)
+    # in the kernel, ``torch.segment_reduce`` on the CPU. (An ``index_add_`` by group id
     # sends every element through an atomic on one of only ``G x H`` addresses — the pattern the reference measured
     # at about half of the GPU time before its segmented-sum kernel, pithtrain/operators/indexed_bias_add.py:7-13.)
     # Rows at or past ``offs[-1]`` belong to no group and are not read; ``unsafe`` skips the host-side length check.
+    H = x.shape[-1]
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and H % 2 == 0 and x.is_contiguous():
+        out = torch.empty((num_groups, H), dtype=torch.float32, device=x.device)
+        wf = None if row_w is None else row_w.float().contiguous()
+        rc = _native.lib().pt_segment_sum(x.data_ptr(), int(x.dtype == torch.float32), _native.ptr(wf),
+                                          offs.data_ptr(), num_groups, out.data_ptr(), H, sp())
+        _native.check(rc, "pt_segment_sum")
+        return out
+    xf = x.float() if row_w is None else x.float() * row_w.float()[:, None]
     o = offs[:num_groups + 1].long()
-    return torch.segment_reduce(x.float(), "sum", lengths=o[1:] - o[:-1], axis=0, unsafe=True)
+    return torch.segment_reduce(xf, "sum", lengths=o[1:] - o[:-1], axis=0, unsafe=True)
+
+
+def indexed_bias_add_rows(x: torch.Tensor, bias: torch.Tensor, offs: torch.Tensor, n_rows: Optional[torch.Tensor] = None,
+                          inplace: bool = False) -> torch.Tensor:
+    """``x[r] + bias[group(r)]`` for expert-sorted rows (groups from ``offs[E+1]``); rows past ``n_rows`` are left
+    as they are. One kernel (binary search of the group per row) instead of arange / bucketize / index / add."""
+    E, H = bias.shape
+    if use_native(x) and bias.dtype == torch.bfloat16 and H % 8 == 0 and x.is_contiguous() and bias.is_contiguous():
+        out = x if inplace else torch.empty_like(x)
+        rc = _native.lib().pt_indexed_bias_add(x.data_ptr(), bias.data_ptr(), offs.data_ptr(), E, out.data_ptr(),
+                                               _native.ptr(n_rows), x.shape[0], H, sp())
+        _native.check(rc, "pt_indexed_bias_add")
+        return out
+    gid = rows_group_id(offs, x.shape[0]).clamp(max=E - 1)
+    return x + bias[gid].to(x.dtype)
 
 
 def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
@@ -273,10 +299,8 @@ class _MoEExpertsFn(torch.autograd.Function):
         else:
             xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
             gu = G.grouped_gemm_nt(xs, ew.w1, offs)
-        gid = None
         if ew.b1 is not None:
-            gid = rows_group_id(offs, gu.shape[0]).clamp(max=E - 1)
-            gu = gu + ew.b1.detach()[gid].to(gu.dtype)
+            gu = indexed_bias_add_rows(gu, ew.b1.detach(), offs, n_rows, inplace=True)
         act = swiglu_fwd(gu, n_rows, ew.interleaved, ew.alpha, ew.limit)
         if fp8:
             q2, s2, _, _ = F8.quantized_weight(ew.w2)
@@ -286,7 +310,7 @@ class _MoEExpertsFn(torch.autograd.Function):
         else:
             y = G.grouped_gemm_nt(act, ew.w2, offs)
         if ew.b2 is not None:
-            y = y + ew.b2.detach()[gid].to(y.dtype)
+            y = indexed_bias_add_rows(y, ew.b2.detach(), offs, n_rows, inplace=True)
         out = combine_rows(y, row_of_slot, k, w=w)
         ctx.save_for_backward(x, w, gu, offs, row_of_slot, slot_of_row)
         ctx.ew = ew
@@ -328,7 +352,7 @@ class _MoEExpertsFn(torch.autograd.Function):
             # y = act @ W2.T + b2 ; the routing-weight gradient also sees the bias term
             gid = rows_group_id(offs, gu.shape[0]).clamp(max=E - 1)
             d_row_w = d_row_w + (dyg.float() * ew.b2.detach()[gid].float()).sum(-1)
-            accumulate_grad(ew.b2, segment_sum(dyg.float() * row_w[:, None], offs, E))
+            accumulate_grad(ew.b2, segment_sum(dyg, offs, E, row_w=row_w))
         if ew.b1 is not None:
             accumulate_grad(ew.b1, segment_sum(dgu, offs, E))
         if plain:

@@ -352,3 +352,43 @@ def test_newton_schulz_on_own_gemms_matches_library_products(shape):
         os.environ["PITHTRAIN_NS_GEMM"] = "own"
     assert got.shape == want.shape
     assert float((got - want).norm() / want.norm()) < 0.05
+
+
+@pytest.mark.parametrize("E,H", [(4, 256), (32, 2880), (1, 64)])
+def test_indexed_bias_add_and_segment_sum_kernels(E, H):
+    """Per-expert bias on expert-sorted rows and its segmented gradient against plain tensor ops."""
+    from pithtrain_b200.ops import moe as M
+    from pithtrain_b200.ops.activations import indexed_bias_add
+
+    torch.manual_seed(31)
+    sizes = torch.randint(0, 70, (E,))
+    sizes[0] = 0 if E > 1 else 40                       # an empty group must work
+    offs = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(((sizes + 15) // 16) * 16, 0)]).int().cuda()
+    R = int(offs[-1]) + 32                              # rows past offs[E] belong to no group
+    x = bf(R, H, scale=1.0)
+    bias = torch.nn.Parameter(bf(E, H, scale=1.0))
+    gid = M.rows_group_id(offs, R).clamp(max=E - 1)
+    n_rows = offs[E:E + 1]
+    got = M.indexed_bias_add_rows(x, bias.detach(), offs, n_rows)
+    want = x + bias.detach()[gid]
+    last = int(offs[-1])
+    assert torch.equal(got[:last], want[:last])
+    # segmented sums, plain and row-weighted, bf16 and fp32 inputs
+    w = torch.rand(R, device="cuda")
+    o = offs.long()
+    for src in (x, x.float()):
+        for rw in (None, w):
+            s = M.segment_sum(src, offs, E, row_w=rw)
+            xf = src.float() if rw is None else src.float() * rw[:, None]
+            ref = torch.stack([xf[o[g]:o[g + 1]].sum(0) for g in range(E)])
+            assert torch.allclose(s, ref, atol=2e-3, rtol=1e-4)
+    # the autograd op: bias gradient = per-group row sum of the incoming gradient
+    xg = x[:last].clone().requires_grad_()
+    y = indexed_bias_add(xg, bias, offs)
+    go = bf(last, H, scale=1.0)
+    y.backward(go)
+    _native.check_status()
+    ref_b = torch.stack([go.float()[o[g]:o[g + 1]].sum(0) for g in range(E)])
+    grad = bias.grad if bias.grad is not None else bias.main_grad
+    assert torch.allclose(grad.float(), ref_b, atol=0.3, rtol=2e-2)
+    assert torch.equal(xg.grad, go)
