@@ -122,6 +122,8 @@ def main() -> int:
     ap.add_argument("--optimizer", default="muon")
     ap.add_argument("--resident-state-gb", type=float, default=22.0,
                     help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
+    ap.add_argument("--state-dtype", choices=["auto", "fp32", "bf16"], default="auto",
+                    help="gradient accumulators and Muon momentum: auto = fp32 from 2 GPUs on (the reference's precision), bf16 on one GPU")
     ap.add_argument("--fp8", action="store_true", help="not the headline run: forward/dgrad GEMMs in block-scaled e4m3 (dtype says so)")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
     ap.add_argument("--routing", choices=["natural", "balanced"], default="natural",
@@ -160,9 +162,14 @@ def main() -> int:
     t.optimizer = make_muon_optimizer if args.optimizer == "muon" else make_adamw_optimizer
     t.scheduler = make_constant_scheduler
     t.dataset = None  # synthetic uniform token ids
-    t.grad_dtype = "bf16"
+    # Optimizer-state precision: the reference accumulates gradients and keeps Muon momentum in fp32
+    # (pithtrain/modules/training.py:349-354, modules/optimizer.py:193-200). From 2 GPUs on the benchmark does the same.
+    # One GPU cannot hold the 30B model with fp32 accumulators (61 GB of bf16 parameters + 122 GB of fp32 gradients
+    # exceed 180 GB), so N = 1 runs bf16 accumulators and bf16 momentum, and says so in "config".
+    wide = n >= 2 if args.state_dtype == "auto" else args.state_dtype == "fp32"
+    t.grad_dtype = "fp32" if wide else "bf16"
     t.fp8 = bool(args.fp8)
-    t.muon_momentum_dtype = "bf16"
+    t.muon_momentum_dtype = "fp32" if wide else "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
     t.num_hidden_layers_override = args.layers

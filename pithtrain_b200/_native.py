@@ -15,7 +15,10 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libpithb200.so"
+# PITHTRAIN_CHECKED_LIB=1 loads the bounds-checking build (python -m pithtrain_b200.build --bounds-check): a
+# diagnostic like a sanitizer run, slower, same entry points.
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / (
+    "libpithb200_checked.so" if __import__("os").environ.get("PITHTRAIN_CHECKED_LIB") == "1" else "libpithb200.so")
 
 
 class NativeLibraryMissing(RuntimeError):
@@ -34,6 +37,7 @@ STATUS_NAMES = {
     5: "receive-buffer capacity exceeded",
     6: "timeout draining in-flight copies",
     7: "dynamic shared memory not 1024-byte aligned",
+    8: "index out of bounds (bounds-checking build)",
 }
 
 

@@ -47,10 +47,11 @@ def lib_path() -> Path:
     return LIBDIR / LIBNAME
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile and link the library; returns its path."""
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, bounds_check: bool = False) -> Path:
+    """Compile and link the library; returns its path. ``bounds_check`` builds ``libpithb200_checked.so`` with
+    ``-DPT_BOUNDS_CHECK`` (index validation in the kernels that address memory through device-computed indices)."""
     LIBDIR.mkdir(exist_ok=True)
-    objdir = LIBDIR / "obj"
+    objdir = LIBDIR / ("obj_checked" if bounds_check else "obj")
     objdir.mkdir(exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     hdr_m = _newest_header_mtime()
@@ -59,7 +60,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         obj = objdir / (src.stem + ".o")
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
         if stale:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [_nvcc(), *NVCC_FLAGS, *(["-DPT_BOUNDS_CHECK"] if bounds_check else []), "-c", str(src), "-o", str(obj)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append((src, cmd))
@@ -76,7 +77,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
                     sys.stderr.write(f"[build] {src.name}\n{res.stdout}{res.stderr}\n")
                 if res.returncode != 0:
                     raise RuntimeError(f"nvcc failed for {src}")
-    out = lib_path()
+    out = LIBDIR / "libpithb200_checked.so" if bounds_check else lib_path()
     objs = [str(objdir / (s.stem + ".o")) for s in sources]
     need_link = bool(jobs) or not out.exists()
     if need_link:
@@ -89,5 +90,6 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+              bounds_check="--bounds-check" in sys.argv)
     print(p)

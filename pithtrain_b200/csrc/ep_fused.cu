@@ -128,14 +128,16 @@ __global__ void ep_wait_acks_kernel(EpChan c, int slot, unsigned epoch, int* err
 __global__ void __launch_bounds__(256)
 ep_push_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __restrict__ src, long long src_stride,
                const int* __restrict__ send_token_idx, const int* __restrict__ counts,
-               const int* __restrict__ send_eids, const float* __restrict__ weights, int* done) {
+               const int* __restrict__ send_eids, const float* __restrict__ weights, int* done, int* err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int vec = c.W / 16;
   for (int d = 0; d < c.ep; ++d) {
     const int n = counts[d];
+    if (!PT_IN_BOUNDS(n >= 0 && n <= c.cap, err)) continue;
     for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < n; r += gridDim.x * wpb) {
       const int t = send_token_idx[(size_t)d * c.cap + r];
+      if (!PT_IN_BOUNDS(t >= 0 && t < c.cap, err)) continue;  // a partition holds at most one row per token
       const uint4* s4 = reinterpret_cast<const uint4*>(src + (size_t)t * src_stride);
       uint4* d4 = reinterpret_cast<uint4*>(chan_row(c, d, slot, c.rank, r));
       for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
@@ -188,7 +190,7 @@ __global__ void ep_wait_flags_kernel(EpChan c, int slot, unsigned epoch, int* pr
 // Compact the per-source partitions of my channel into dense outputs.
 __global__ void __launch_bounds__(256)
 ep_compact_kernel(EpChan c, int slot, const int* __restrict__ prefix, unsigned char* __restrict__ out_rows,
-                  int* __restrict__ out_eids, float* __restrict__ out_w, int cap_total) {
+                  int* __restrict__ out_eids, float* __restrict__ out_w, int cap_total, int* err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int total = prefix[c.ep];
@@ -198,6 +200,7 @@ ep_compact_kernel(EpChan c, int slot, const int* __restrict__ prefix, unsigned c
       int s = 0;
       while (s + 1 < c.ep && prefix[s + 1] <= i) ++s;
       const int r = i - prefix[s];
+      if (!PT_IN_BOUNDS(r >= 0 && r < c.cap, err)) continue;
       const uint4* s4 = reinterpret_cast<const uint4*>(chan_row(c, c.rank, slot, s, r));
       uint4* d4 = reinterpret_cast<uint4*>(out_rows + (size_t)i * c.W);
       for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
@@ -225,7 +228,7 @@ __global__ void ep_ack_kernel(EpChan c, int slot, unsigned epoch) {
 // rank they came from. `meta_f` optionally carries k floats per row (routing-weight gradients).
 __global__ void __launch_bounds__(256)
 ep_return_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __restrict__ rows,
-                 const float* __restrict__ meta_f, const int* __restrict__ prefix, int* done) {
+                 const float* __restrict__ meta_f, const int* __restrict__ prefix, int* done, int* err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int total = prefix[c.ep];
@@ -234,6 +237,7 @@ ep_return_kernel(EpChan c, int slot, unsigned epoch, const unsigned char* __rest
     int s = 0;
     while (s + 1 < c.ep && prefix[s + 1] <= i) ++s;
     const int r = i - prefix[s];
+    if (!PT_IN_BOUNDS(r >= 0 && r < c.cap, err)) continue;  // the cell the row came from on rank s
     const uint4* s4 = reinterpret_cast<const uint4*>(rows + (size_t)i * c.W);
     uint4* d4 = reinterpret_cast<uint4*>(chan_row(c, s, slot, c.rank, r));
     for (int v = lane; v < vec; v += 32) d4[v] = s4[v];
@@ -277,7 +281,7 @@ PT_API int pt_ep_push(const void* chan, int slot, unsigned epoch, const void* sr
   int* err = device_status_word();
   ep_wait_acks_kernel<<<1, EP_MAX, 0, st>>>(c, slot, epoch, err);
   ep_push_kernel<<<ep_grid(), 256, 0, st>>>(c, slot, epoch, (const unsigned char*)src, src_stride, send_token_idx,
-                                             counts, send_eids, weights, done);
+                                             counts, send_eids, weights, done, err);
   return (int)cudaGetLastError();
 }
 
@@ -288,7 +292,7 @@ PT_API int pt_ep_receive(const void* chan, int slot, unsigned epoch, int* prefix
   EpChan c = *reinterpret_cast<const EpChan*>(chan);
   int* err = device_status_word();
   ep_wait_flags_kernel<<<1, EP_MAX, 0, st>>>(c, slot, epoch, prefix, cap_total, err);
-  ep_compact_kernel<<<ep_grid(), 256, 0, st>>>(c, slot, prefix, (unsigned char*)out_rows, out_eids, out_w, cap_total);
+  ep_compact_kernel<<<ep_grid(), 256, 0, st>>>(c, slot, prefix, (unsigned char*)out_rows, out_eids, out_w, cap_total, err);
   ep_ack_kernel<<<1, EP_MAX, 0, st>>>(c, slot, epoch);
   return (int)cudaGetLastError();
 }
@@ -300,7 +304,7 @@ PT_API int pt_ep_return(const void* chan, int slot, unsigned epoch, const void* 
   if (c.W % 16 != 0) return -1;
   int* err = device_status_word();
   ep_wait_acks_kernel<<<1, EP_MAX, 0, st>>>(c, slot, epoch, err);
-  ep_return_kernel<<<ep_grid(), 256, 0, st>>>(c, slot, epoch, (const unsigned char*)rows, meta_f, prefix, done);
+  ep_return_kernel<<<ep_grid(), 256, 0, st>>>(c, slot, epoch, (const unsigned char*)rows, meta_f, prefix, done, err);
   return (int)cudaGetLastError();
 }
 

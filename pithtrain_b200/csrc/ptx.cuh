@@ -20,7 +20,18 @@ enum : int {
   PT_ERR_CAPACITY = 5,
   PT_ERR_TIMEOUT_DRAIN = 6,
   PT_ERR_SMEM_ALIGN = 7,
+  PT_ERR_BOUNDS = 8,
 };
+
+// Bounds-checking build (-DPT_BOUNDS_CHECK, `python -m pithtrain_b200.build --bounds-check`): kernels that turn
+// device-computed indices into addresses (token indices, receive positions, source ranks of the peer-memory exchanges)
+// validate them first; a bad index is recorded in the status word (PT_ERR_BOUNDS) and the access is skipped instead
+// of corrupting another buffer, possibly on another GPU. The regular build compiles the checks away.
+#ifdef PT_BOUNDS_CHECK
+#define PT_IN_BOUNDS(cond, err) ((cond) ? true : (((err) ? (void)atomicCAS((err), 0, ::pt::PT_ERR_BOUNDS) : (void)0), false))
+#else
+#define PT_IN_BOUNDS(cond, err) true
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

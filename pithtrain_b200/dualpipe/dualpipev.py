@@ -6,8 +6,12 @@ The model is cut into ``2 * pp_size`` stages; rank ``r`` owns stage ``r`` (phase
 (pithtrain/dualpipe/dualpipev.py:83-111,483-655 of the reference). The order of work on each rank is
 data (:func:`pithtrain_b200.dualpipe.schedule.build_schedule`); this module interprets it:
 computes chunks with the 5-stage executor, moves activations between ranks with batched
-isend/irecv (NCCL on GPUs, gloo on CPU) that are posted early and waited for late, and defers
-weight-gradient GEMMs to the W actions through ``WeightGradStore``.
+isend/irecv (NCCL on GPUs, gloo on CPU) and defers weight-gradient GEMMs to the W actions through
+``WeightGradStore``. The sends of an action's outputs and the receive of the next action's input go
+out as one batch at the start of that next action, and the compute stream waits for the batch (the
+reference's ``_commit_and_wait_comm`` discipline, which the deadlock simulator of ``schedule.py``
+covers); the transfer of one ``(micro_batch, seq/cp, hidden)`` activation is not hidden under
+compute.
 
 ``step()`` also serves inference: under ``torch.no_grad()`` only forwards run, and
 ``return_outputs=True`` returns the logits on the rank that owns the last stage (pp rank 0).

@@ -262,6 +262,26 @@ def _from_blob(t: torch.Tensor) -> Any:
     return pickle.loads(t.cpu().numpy().tobytes())
 
 
+def _skeleton_from_keys(md, prefix: str):
+    """Nested lists / dicts with ``None`` leaves for every stored key under ``prefix`` (numeric path parts are list
+    indices); None when nothing is stored there."""
+    paths = [k[len(prefix):].split(".") for k in md if k.startswith(prefix)]
+    if not paths:
+        return None
+
+    def build(items):
+        if any(len(p) == 0 for p in items):
+            return None
+        heads = {}
+        for p in items:
+            heads.setdefault(p[0], []).append(p[1:])
+        if all(h.isdigit() for h in heads):
+            return [build(heads[str(i)]) for i in range(len(heads))]
+        return {h: build(rest) for h, rest in heads.items()}
+
+    return build(paths)
+
+
 def _sched_state(s) -> Dict[str, Any]:
     # LambdaLR keeps its (unpicklable) lambdas out of the state; keep the slot so load_state_dict works
     d = dict(s.state_dict())
@@ -276,8 +296,10 @@ def build_save_state(model: nn.Module, optimizers, schedulers) -> Dict[str, Any]
     optim = to_canonical_optim(optimizers, model)
     optim["state"] = {fqn: {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in st.items()}
                       for fqn, st in optim["state"].items()}
-    optim["param_groups"] = _to_blob(optim["param_groups"])
-    return {"app": {"model": model_state, "optimizer": optim, "scheduler": _to_blob([_sched_state(s) for s in schedulers])}}
+    # param_groups (a list of dicts) and the scheduler states (a list of dicts) hold no tensors: DCP stores each as one
+    # pickled object under ``app.optimizer.param_groups`` / ``app.scheduler`` -- the layout of the reference's AppState
+    # (pithtrain/tasks/pretrain_lm.py:171-191), so either framework reads the other's optimizer section.
+    return {"app": {"model": model_state, "optimizer": optim, "scheduler": [_sched_state(s) for s in schedulers]}}
 
 
 def save_training_checkpoint(cfg) -> Path:
@@ -287,6 +309,10 @@ def save_training_checkpoint(cfg) -> Path:
     assert cfg.training.save_location is not None
     path = checkpoint_dir(cfg.training.save_location, training.step)
     logging.stdout.info("Save checkpoint: %s" % path)
+    if distributed.device.type == "cuda":
+        from ..parallel.symm_mem import check_all_guards
+
+        check_all_guards()  # never persist a state that a stray peer store may have corrupted
     t0 = time.monotonic()
     state = build_save_state(training.model, training.optimizers, training.schedulers)
     dcp.save(state, checkpoint_id=str(path))
@@ -352,7 +378,14 @@ def load_into(path: Path, model: nn.Module, optimizers=(), schedulers=(), strict
         for key, holder, name in (("app.optimizer.param_groups", request["app"]["optimizer"], "param_groups"),
                                   ("app.scheduler", request["app"], "scheduler")):
             if key in md and hasattr(md[key], "size"):
+                # written by an earlier version of this package: one uint8 tensor holding the pickled object
                 holder[name] = torch.empty(tuple(md[key].size), dtype=torch.uint8)
+            else:
+                # DCP flattens lists of dicts field by field (``app.scheduler.0.last_epoch`` ...): rebuild the nesting
+                # from the stored keys with placeholders that the load fills in
+                skel = _skeleton_from_keys(md, key + ".")
+                if skel is not None:
+                    holder[name] = skel
     dcp.load(request, checkpoint_id=str(path))
     if not model_only and optimizers:
         opt_req = request["app"]["optimizer"]

@@ -51,8 +51,8 @@ class PayloadExchange:
                 n *= x
             off = _align(off + n * torch.empty((), dtype=dt).element_size())
         self.slot_bytes = off
-        self.buf = SymmetricBuffer(2 * self.slot_bytes, group, device)
-        self.ctl = SymmetricBuffer(CTL_WORDS * 4, group, device)
+        self.buf = SymmetricBuffer(2 * self.slot_bytes, group, device, "context-parallel payload")
+        self.ctl = SymmetricBuffer(CTL_WORDS * 4, group, device, "context-parallel control")
         self._ctl_ptrs = (ctypes.c_void_p * cp)(*self.ctl.peer_ptrs)
         self.with_grads = with_grads
         if with_grads:
@@ -64,7 +64,7 @@ class PayloadExchange:
                     n *= x
                 off = _align(off + n * 4)
             self.g_part_bytes = off
-            self.gbuf = SymmetricBuffer(2 * cp * self.g_part_bytes, group, device)
+            self.gbuf = SymmetricBuffer(2 * cp * self.g_part_bytes, group, device, "context-parallel gradients")
         self.epoch = 0
         self.side = torch.cuda.Stream(device=device)
 

@@ -58,7 +58,7 @@ class Channel:
         self.off_flag = off; off = _align(off + 2 * ep * 4)
         self.off_ack = off; off = _align(off + 2 * ep * 4)
         self.off_done = off; off = _align(off + 64)
-        self.buf = SymmetricBuffer(off, group, device)
+        self.buf = SymmetricBuffer(off, group, device, "expert-parallel channel")
         s = EpChanStruct()
         s.ep, s.rank, s.cap, s.W, s.k = ep, rank, cap, row_bytes, k
         s.off_data, s.off_mi, s.off_mf = self.off_data, self.off_mi, self.off_mf

@@ -45,9 +45,9 @@ class FusedShardComm:
         total = region * group_size
         pbytes = torch.empty((), dtype=param_dtype).element_size()
         gbytes = torch.empty((), dtype=grad_dtype).element_size()
-        self.param_buf = SymmetricBuffer(total * pbytes, group, device)
-        self.grad_buf = SymmetricBuffer(total * gbytes, group, device)
-        self.ctl_buf = SymmetricBuffer(L.pt_fsdp_ctl_bytes(), group, device)
+        self.param_buf = SymmetricBuffer(total * pbytes, group, device, "shard parameters")
+        self.grad_buf = SymmetricBuffer(total * gbytes, group, device, "shard gradients")
+        self.ctl_buf = SymmetricBuffer(L.pt_fsdp_ctl_bytes(), group, device, "shard control")
         self.flat_param = self.param_buf.view(0, (total,), param_dtype)
         self.flat_grad = self.grad_buf.view(0, (total,), grad_dtype)
         s = FsdpChanStruct()

@@ -58,3 +58,38 @@ def run(rank: int, world: int, m: int, H: int, E: int, k: int, rounds: int = 3):
         assert torch.allclose(gw1, gw2, atol=5e-1, rtol=3e-2), float((gw1 - gw2).abs().max())
     dist.barrier()
     fused.close()
+
+
+def run_checked(rank: int, world: int, m: int, H: int, E: int, k: int):
+    """Bounds-checking build of the library: a corrupted send plan (a token index one past the micro-batch) is
+    recorded in the status word and the row is skipped, instead of a read outside the activations and a store of
+    garbage into the peer's partition."""
+    import os
+
+    os.environ["PITHTRAIN_CHECKED_LIB"] = "1"
+    from pithtrain_b200 import _native
+    from pithtrain_b200.contexts import distributed
+    from pithtrain_b200.modules.distributed import DistributedCfg, setup_distributed
+    from pithtrain_b200.parallel.ep_fused import FusedExchange
+
+    assert _native._LIB_PATH.name == "libpithb200_checked.so", _native._LIB_PATH
+    cfg = SimpleNamespace(distributed=DistributedCfg())
+    cfg.distributed.expert_parallel_size = world
+    setup_distributed(cfg, failfast=False)
+    dev = distributed.device
+    fused = FusedExchange(distributed.ep_group, world, rank)
+    g = torch.Generator(device="cpu").manual_seed(200 + rank)
+    x = torch.randn(m, H, generator=g).to(dev).bfloat16()
+    w = torch.rand(m, k, generator=g).to(dev)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(m)]).int().to(dev)
+    plan = fused.plan(idx, E)
+    rx, _ = fused.dispatch(x, w, plan)      # a clean exchange first
+    torch.cuda.synchronize()
+    assert _native.fetch_status() == 0
+    plan = fused.plan(idx, E)
+    plan.send_token_idx[0] = m              # one past the last token
+    fused.dispatch(x, w, plan)
+    torch.cuda.synchronize()
+    assert _native.fetch_status() == 8      # PT_ERR_BOUNDS
+    dist.barrier()
+    fused.close()

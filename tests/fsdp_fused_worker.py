@@ -51,6 +51,21 @@ def run(rank: int, world: int, grad_dtype_name: str, rounds: int = 3):
         assert torch.equal(fused.flat_param, base.flat_param), it
         assert float(fused.flat_grad.abs().max()) == 0.0
     dist.barrier()
+    # guard words behind every symmetric allocation: intact after the exchanges, and a write behind the buffer (what an
+    # out-of-range peer store would do; made from the host side here) is reported with the buffer's name
+    from pithtrain_b200.parallel.symm_mem import GuardOverrun, check_all_guards
+
+    check_all_guards()
+    saved = int(fused.comm.grad_buf._guard[3])
+    fused.comm.grad_buf._guard[3] = 0
+    try:
+        check_all_guards()
+    except GuardOverrun as e:
+        assert "shard gradients" in str(e), str(e)
+    else:
+        raise AssertionError("an overwritten guard word went unnoticed")
+    fused.comm.grad_buf._guard[3] = saved
+    dist.barrier()
     fused.comm.close()
     if rounds >= 3 and gdt == torch.bfloat16:
         _report_bandwidth(rank, world, dev)

@@ -40,3 +40,15 @@ def test_qwen3_ep2_fused_transport():
 def test_qwen3_pp2_ep2_fused_transport_four_gpus():
     _need(4)
     launch(4, dualpipev_worker.run, "qwen3_gpu", 2, 2, 5, True, "cuda", "fused", backend="nccl")
+
+
+def test_bounds_checking_build_catches_a_corrupted_send_plan():
+    """The -DPT_BOUNDS_CHECK build of the library (pithtrain_b200/_lib/libpithb200_checked.so)."""
+    from pathlib import Path
+
+    _need(2)
+    import ep_fused_worker
+
+    if not (Path(__file__).resolve().parents[1] / "pithtrain_b200" / "_lib" / "libpithb200_checked.so").exists():
+        pytest.skip("bounds-checking build not present: python -m pithtrain_b200.build --bounds-check")
+    launch(2, ep_fused_worker.run_checked, 256, 512, 8, 2, backend="nccl")

@@ -458,3 +458,23 @@ def test_new_entry_points_validate_their_arguments_on_the_host():
     assert bwd(256, 4, 2, 128) == -3
     assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 60, 60, 60, 256, N) == -2  # K not a multiple of 8
     assert L.pt_gemm2cta_nt(N, N, N, 256, 256, 64, 64, 64, 256, N) == -3
+
+
+def test_bounds_checking_variant_compiles():
+    """``-DPT_BOUNDS_CHECK`` turns the index validation of the peer-memory exchange kernels on; the variant must keep
+    compiling for sm_100a (the regular build compiles the checks away)."""
+    import shutil
+    import subprocess
+    import tempfile
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(nvcc).exists():
+        pytest.skip("no nvcc")
+    from pithtrain_b200 import build as B
+
+    src = ROOT / "pithtrain_b200" / "csrc" / "ep_fused.cu"
+    with tempfile.TemporaryDirectory() as d:
+        res = subprocess.run([nvcc, *B.NVCC_FLAGS, "-DPT_BOUNDS_CHECK", "-c", str(src), "-o", str(Path(d) / "x.o")],
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr[-2000:]
+    assert "PT_IN_BOUNDS" in src.read_text()
