@@ -163,20 +163,25 @@ def main() -> int:
     t.scheduler = make_constant_scheduler
     t.dataset = None  # synthetic uniform token ids
     # Optimizer-state precision: the reference accumulates gradients and keeps Muon momentum in fp32
-    # (pithtrain/modules/training.py:349-354, modules/optimizer.py:193-200). From 2 GPUs on the benchmark does the same.
-    # One GPU cannot hold the 30B model with fp32 accumulators (61 GB of bf16 parameters + 122 GB of fp32 gradients
-    # exceed 180 GB), so N = 1 runs bf16 accumulators and bf16 momentum, and says so in "config".
-    wide = n >= 2 if args.state_dtype == "auto" else args.state_dtype == "fp32"
-    t.grad_dtype = "fp32" if wide else "bf16"
+    # (pithtrain/modules/training.py:349-354, modules/optimizer.py:193-200). The benchmark does the same wherever the
+    # state fits in 180 GB per GPU and says what it ran in "config":
+    #   N >= 4: fp32 gradient accumulators and fp32 momentum;
+    #   N = 2 : fp32 accumulators (64 GB per GPU) and bf16 momentum (fp32 momentum, 58 GB more, does not fit);
+    #   N = 1 : bf16 accumulators and bf16 momentum (61 GB of parameters + 122 GB of fp32 gradients exceed one GPU).
+    if args.state_dtype == "auto":
+        grads_wide, mom_wide = n >= 2, n >= 4
+    else:
+        grads_wide = mom_wide = args.state_dtype == "fp32"
+    t.grad_dtype = "fp32" if grads_wide else "bf16"
     t.fp8 = bool(args.fp8)
-    t.muon_momentum_dtype = "fp32" if wide else "bf16"
+    t.muon_momentum_dtype = "fp32" if mom_wide else "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
     t.num_hidden_layers_override = args.layers
     t.benchmark = args.routing == "balanced"
 
     setup_logging(cfg)
-    setup_distributed(cfg, failfast=False)
+    setup_distributed(cfg, failfast=True)  # a rank that dies (e.g. out of memory) takes the job down at once
     setup_training(cfg)
     dev = distributed.device
     rank = distributed.rank

@@ -102,6 +102,7 @@ def backward(do, q, k, v, out, lse, scale: float, causal: bool, q_off: int, row_
     from .. import _native
 
     q, k, v, do, out = (_as_token_major(t) for t in (q, k, v, do, out))
+    lse = lse.contiguous()  # ring attention hands in halves of a longer sequence's statistics
     B, Sq, Hq, D = q.shape
     Sk, Hkv, Dv = k.shape[1], k.shape[2], v.shape[-1]
     # fp32 accumulators (dq over key tiles; dk / dv over the heads of a GQA group), zeroed in one memset
