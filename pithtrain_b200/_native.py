@@ -116,6 +116,8 @@ SIGS = {
     "pt_attn_fwd": "PPPPPPP" + "IIIIIII" + "LLLL" + "F" + "II" + "P",
     "pt_attn_bwd": "PPPPPPPPPPPPPPP" + "IIIIII" + "LLLLL" + "F" + "II" + "P",
     "pt_gemm2cta_nt": "PPPIIILLLP",
+    "pt_gdr_state_fwd": "PPPPPPPPIIIIP",
+    "pt_gdr_state_bwd": "PPPPPPPPPPPPPIIIIP",
 }
 
 _CT = {"P": c_void_p, "I": c_int, "L": c_longlong, "F": c_float}

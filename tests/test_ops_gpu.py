@@ -392,3 +392,34 @@ def test_indexed_bias_add_and_segment_sum_kernels(E, H):
     grad = bias.grad if bias.grad is not None else bias.main_grad
     assert torch.allclose(grad.float(), ref_b, atol=0.3, rtol=2e-2)
     assert torch.equal(xg.grad, go)
+
+
+@pytest.mark.parametrize("B,S,H,dk,dv", [(1, 256, 4, 128, 128), (2, 200, 2, 64, 64), (1, 1024, 8, 128, 128)])
+def test_gated_delta_rule_recurrence_kernels(B, S, H, dk, dv):
+    """The chunk-to-chunk pass of the gated delta rule on the kernels of csrc/gdr.cu (forward and backward) against the
+    same pass in tensor ops, and the whole op against the token-by-token recurrence."""
+    from pithtrain_b200.ops import gated_delta_rule as GD
+
+    torch.manual_seed(41)
+    N, C = (S + 63) // 64, 64
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.3).requires_grad_()
+    w, qg, kd = mk(B, H, N, C, dk), mk(B, H, N, C, dk), mk(B, H, N, C, dk)
+    u = mk(B, H, N, C, dv)
+    a = (torch.rand(B, H, N, device="cuda") * 0.5 + 0.5).requires_grad_()
+    go_v, go_o = torch.randn(B, H, N, C, dv, device="cuda"), torch.randn(B, H, N, C, dv, device="cuda")
+    outs = []
+    for fn in (GD._ChunkState.apply, GD._chunk_state_math):
+        v_new, o_inter = fn(w, u, qg, kd, a)
+        grads = torch.autograd.grad((v_new, o_inter), [w, u, qg, kd, a], (go_v, go_o))
+        outs.append((v_new, o_inter) + grads)
+    _native.check_status()
+    for x, y in zip(*outs):
+        assert torch.allclose(x, y, atol=2e-3, rtol=2e-3), float((x - y).abs().max())
+    # the whole op in bf16 against the recurrence
+    q, k = bf(B, S, H, dk, scale=1.0), torch.nn.functional.normalize(torch.randn(B, S, H, dk, device="cuda"), dim=-1).bfloat16()
+    v = bf(B, S, H, dv, scale=1.0)
+    g = -torch.rand(B, S, H, device="cuda") * 0.2
+    beta = torch.rand(B, S, H, device="cuda")
+    got = GD.gated_delta_rule(q, k, v, g, beta)
+    ref = GD.gated_delta_rule_recurrent(q, k, v, g, beta)
+    assert calc_diff(got.float(), ref.float()) < 1e-3
