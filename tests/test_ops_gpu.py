@@ -402,7 +402,7 @@ def test_gated_delta_rule_recurrence_kernels(B, S, H, dk, dv):
 
     torch.manual_seed(41)
     N, C = (S + 63) // 64, 64
-    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.3).requires_grad_()
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).requires_grad_()  # small: the state must not blow up over N chunks
     w, qg, kd = mk(B, H, N, C, dk), mk(B, H, N, C, dk), mk(B, H, N, C, dk)
     u = mk(B, H, N, C, dv)
     a = (torch.rand(B, H, N, device="cuda") * 0.5 + 0.5).requires_grad_()
@@ -414,7 +414,7 @@ def test_gated_delta_rule_recurrence_kernels(B, S, H, dk, dv):
         outs.append((v_new, o_inter) + grads)
     _native.check_status()
     for x, y in zip(*outs):
-        assert torch.allclose(x, y, atol=2e-3, rtol=2e-3), float((x - y).abs().max())
+        assert calc_diff(x, y) < 1e-6, calc_diff(x, y)
     # the whole op in bf16 against the recurrence
     q, k = bf(B, S, H, dk, scale=1.0), torch.nn.functional.normalize(torch.randn(B, S, H, dk, device="cuda"), dim=-1).bfloat16()
     v = bf(B, S, H, dv, scale=1.0)
