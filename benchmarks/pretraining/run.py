@@ -18,6 +18,8 @@ def main() -> None:
     ap.add_argument("mesh", nargs="?")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--max-steps", type=int, default=25)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="debug only: truncate the model to this many layers (a run with it is no benchmark number)")
     a = ap.parse_args()
     if a.list or not a.model:
         for name, r in MODELS.items():
@@ -27,6 +29,8 @@ def main() -> None:
     mesh = a.mesh or MODELS[a.model].meshes[0]
     cfg = make_cfg(a.model, mesh)
     cfg.training.max_steps = a.max_steps
+    if a.layers is not None:
+        cfg.training.num_hidden_layers_override = a.layers
     from pithtrain_b200.tasks.pretrain_lm import launch
 
     launch(cfg)
