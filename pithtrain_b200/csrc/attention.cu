@@ -28,14 +28,11 @@ namespace pt {
 
 constexpr int AT_SLAB = 128 * 64 * 2;      // one [128 x 64] bf16 swizzle slab: 16 KB
 constexpr float AT_RESCALE_LOG2 = 8.0f;    // tolerated growth of a row maximum before O is rescaled
-#ifndef AT_SCALAR_EXP
-#define AT_SCALAR_EXP 0
-#endif
 #ifndef AT_POLY_MASK
-// Which of every 8 element pairs take the polynomial exp2 (bit i = pair i). 0: all exponentials on the special-function
-// unit. Shares of 25..75 % measured no faster on B200 at head dim 128 (the integer half of the polynomial path lands on
-// the half-rate ALU pipe), so the default is off; the path stays for head dims where the balance differs.
-#define AT_POLY_MASK 0x0u
+// Which of every 8 scores take the polynomial exp2 on the FMA pipe instead of the special-function unit (bit i =
+// element i mod 8). The special-function unit delivers ~8 exponentials per clock per SM, the tensor core consumes
+// 128 x 128 of them per ~1000 cycles per tile: the split balances the two pipes.
+#define AT_POLY_MASK 0xB5u
 #endif
 
 struct AttnArgs {
@@ -69,7 +66,6 @@ struct AttnFwdCfg {
 // element pairs are evaluated by polynomial on the FMA pipe instead of the special-function unit.
 template <uint32_t POLY>
 __device__ __forceinline__ float softmax_exp_store(const uint32_t (&sv)[128], float scale_log2, float m_use, uint32_t tS) {
-#if AT_SCALAR_EXP
   float l4[4] = {0.f, 0.f, 0.f, 0.f};
   const float nm = -m_use;
 #pragma unroll
@@ -77,8 +73,11 @@ __device__ __forceinline__ float softmax_exp_store(const uint32_t (&sv)[128], fl
     uint32_t w[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), scale_log2, nm));
-      const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), scale_log2, nm));
+      const float x0 = fmaf(__uint_as_float(sv[c * 32 + 2 * i]), scale_log2, nm);
+      const float x1 = fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), scale_log2, nm);
+      // POLY bit (2i mod 8) / (2i+1 mod 8): which elements of every 8 go to the FMA pipe
+      const float e0 = (POLY & (1u << ((2 * i) & 7))) ? exp2_poly(x0) : ex2_approx(x0);
+      const float e1 = (POLY & (1u << ((2 * i + 1) & 7))) ? exp2_poly(x1) : ex2_approx(x1);
       l4[(2 * i) & 3] += e0;
       l4[(2 * i + 1) & 3] += e1;
       w[i] = pack_bf16x2(e0, e1);
@@ -86,32 +85,6 @@ __device__ __forceinline__ float softmax_exp_store(const uint32_t (&sv)[128], fl
     tmem_st_32x16(tS + c * 16, w);
   }
   return (l4[0] + l4[1]) + (l4[2] + l4[3]);
-#else
-  const uint64_t SC2 = f2_pack(scale_log2, scale_log2), NM2 = f2_pack(-m_use, -m_use);
-  uint64_t L2a = f2_pack(0.f, 0.f), L2b = L2a;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t w[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float x0, x1, e0, e1;
-      f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + 2 * i]), __uint_as_float(sv[c * 32 + 2 * i + 1])), SC2, NM2), x0, x1);
-      if (POLY & (1u << (i & 7))) {
-        exp2_poly_pair(x0, x1, e0, e1);
-      } else {
-        e0 = ex2_approx(x0);
-        e1 = ex2_approx(x1);
-      }
-      if (i & 1) L2b = f2_add(L2b, f2_pack(e0, e1)); else L2a = f2_add(L2a, f2_pack(e0, e1));
-      w[i] = pack_bf16x2(e0, e1);
-    }
-    tmem_st_32x16(tS + c * 16, w);
-  }
-  float a0, a1, b0, b1;
-  f2_unpack(L2a, a0, a1);
-  f2_unpack(L2b, b0, b1);
-  return (a0 + a1) + (b0 + b1);
-#endif
 }
 
 template <int DQK, int DV, int NQ, int KST>

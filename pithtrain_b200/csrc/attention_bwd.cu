@@ -29,6 +29,9 @@
 namespace pt {
 
 constexpr int AB_SLAB = 128 * 64 * 2;  // one [128 x 64] bf16 swizzle slab: 16 KB
+#ifndef AB_POLY_MASK
+#define AB_POLY_MASK 0xB5u  // which of every 8 exponentials take the polynomial on the FMA pipe (see exp2_poly)
+#endif
 
 struct AttnBwdArgs {
   int B, Sq, Sk, Hq, Hkv;
@@ -342,10 +345,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
           const float4 ls = *reinterpret_cast<const float4*>(st_lse + u * 4);
-          float p0 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y));
-          float p2 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z));
-          float p3 = ex2_approx(fmaf(__uint_as_float(sv[4 * u + 3]), args.scale_log2, -ls.w));
+          // five of every eight exponentials on the FMA pipe (polynomial), three on the special-function unit: the
+          // latter's rate, not the arithmetic, bounds this phase otherwise
+          const float x0 = fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x);
+          const float x1 = fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y);
+          const float x2 = fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z);
+          const float x3 = fmaf(__uint_as_float(sv[4 * u + 3]), args.scale_log2, -ls.w);
+          float p0 = (AB_POLY_MASK & (1u << ((4 * u + 0) & 7))) ? exp2_poly(x0) : ex2_approx(x0);
+          float p1 = (AB_POLY_MASK & (1u << ((4 * u + 1) & 7))) ? exp2_poly(x1) : ex2_approx(x1);
+          float p2 = (AB_POLY_MASK & (1u << ((4 * u + 2) & 7))) ? exp2_poly(x2) : ex2_approx(x2);
+          float p3 = (AB_POLY_MASK & (1u << ((4 * u + 3) & 7))) ? exp2_poly(x3) : ex2_approx(x3);
           if (need_mask) {
             const int qr = q0 + 4 * u;
             const float pv[4] = {p0, p1, p2, p3};

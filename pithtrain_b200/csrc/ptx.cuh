@@ -413,22 +413,22 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for a pair without the special-function unit: round-to-nearest split x = n + f, |f| <= 0.5, degree-3 polynomial
-// for 2^f (relative error 7.5e-5, below bf16 resolution), exponent added with integer arithmetic. x is clamped at
-// -126, where the result is ~1.2e-38 instead of 0; callers that need exact zeros use ex2.approx for those elements.
-__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& e0, float& e1) {
-  const uint64_t X = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t FI = f2_add(X, f2_pack(12582912.f, 12582912.f));
-  const uint64_t Nn = f2_add(FI, f2_pack(-12582912.f, -12582912.f));
-  const uint64_t F = f2_fma(Nn, f2_pack(-1.f, -1.f), X);
-  uint64_t P = f2_fma(F, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
-  P = f2_fma(P, F, f2_pack(0.6932609677f, 0.6932609677f));
-  P = f2_fma(P, F, f2_pack(0.9999280572f, 0.9999280572f));
-  float p0, p1, fi0, fi1;
-  f2_unpack(P, p0, p1);
-  f2_unpack(FI, fi0, fi1);
-  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(fi0) << 23));
-  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(fi1) << 23));
+// 2^x without the special-function unit (whose rate, ~8 results per clock per SM, is what bounds the softmax of an
+// attention tile: the tensor core needs 128 x 128 exponentials every ~1000 cycles): round-to-nearest split x = n + f,
+// |f| <= 0.5, degree-3 polynomial for 2^f (relative error 7.5e-5, below bf16 resolution), and the exponent added to
+// the polynomial's bits with one integer multiply-add. Everything except the clamp runs on the FMA pipe. x is
+// clamped at -126, where the result is ~1.2e-38 instead of 0; callers that need exact zeros (masked scores) use
+// ex2_approx for those tiles.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float fi = x + 12582912.f;        // 1.5 * 2^23: the low mantissa bits of fi hold round(x)
+  const float f = x - (fi - 12582912.f);
+  float p = fmaf(f, 0.0551716685f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  uint32_t r;
+  asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(__float_as_uint(fi)), "r"(1u << 23), "r"(__float_as_uint(p)));
+  return __uint_as_float(r);
 }
 
 // ----------------------------------------------------------------------------------------------
