@@ -124,6 +124,8 @@ def main() -> int:
                     help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
     ap.add_argument("--state-dtype", choices=["auto", "fp32", "bf16"], default="auto",
                     help="gradient accumulators and Muon momentum: auto = fp32 from 2 GPUs on (the reference's precision), bf16 on one GPU")
+    ap.add_argument("--pair-wgrads", choices=["auto", "on", "off"], default="auto",
+                    help="expert weight gradients of two micro-batches per launch (auto: from 2 GPUs on, where fp32 accumulators make the pass over them costly)")
     ap.add_argument("--fp8", action="store_true", help="not the headline run: forward/dgrad GEMMs in block-scaled e4m3 (dtype says so)")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
     ap.add_argument("--routing", choices=["natural", "balanced"], default="natural",
@@ -177,6 +179,7 @@ def main() -> int:
     t.muon_momentum_dtype = "fp32" if mom_wide else "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
+    t.pair_expert_wgrads = (n >= 2) if args.pair_wgrads == "auto" else args.pair_wgrads == "on"
     t.num_hidden_layers_override = args.layers
     t.benchmark = args.routing == "balanced"
 
@@ -263,7 +266,7 @@ def main() -> int:
                 "global_batch": t.global_batch_size, "global_batch_tokens": tokens_per_step, "seq_len": SEQ_LEN,
                 "micro_batch": 1, "parallelism": f"pp{pp}xcp{cp}xep{ep}xdp{distributed.dp_size}",
                 "optimizer": "Muon (2-D/expert weights) + AdamW (rest), grad clip 1.0" if args.optimizer == "muon" else "AdamW",
-                "grad_accumulators": t.grad_dtype, "muon_momentum": t.muon_momentum_dtype + (f", {t.optimizer_device_state_gb:.0f} GiB resident + the rest in pinned host memory (streamed each step)" if t.offload_optimizer_state else ""),
+                "grad_accumulators": t.grad_dtype, "paired_expert_wgrads": t.pair_expert_wgrads, "muon_momentum": t.muon_momentum_dtype + (f", {t.optimizer_device_state_gb:.0f} GiB resident + the rest in pinned host memory (streamed each step)" if t.offload_optimizer_state else ""),
                 "routing": ("natural (seeded random-init gate)" if args.routing == "natural"
                             else "force-balanced round-robin replay (benchmark mode)"), "ep_transport": args.ep_backend,
                 "l2": "inputs larger than L2: every step streams >10 GB of parameters and activations, no explicit flush",

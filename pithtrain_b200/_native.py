@@ -61,6 +61,7 @@ SIGS = {
     "pt_sm_count": "",
     "pt_set_peer_wait_limit_ns": "L",
     "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIPILP",
+    "pt_gemm_bf16_kgroup2": "PPPLPPPLPIILLLLIIP",
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
     "pt_rmsnorm_bwd": "PPPPPPPIIIP",

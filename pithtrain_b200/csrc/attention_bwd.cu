@@ -30,7 +30,9 @@ namespace pt {
 
 constexpr int AB_SLAB = 128 * 64 * 2;  // one [128 x 64] bf16 swizzle slab: 16 KB
 #ifndef AB_POLY_MASK
-#define AB_POLY_MASK 0xB5u  // which of every 8 exponentials take the polynomial on the FMA pipe (see exp2_poly)
+// Which of every 8 exponentials take the polynomial on the FMA pipe (see exp2_poly). Measured (all five backward
+// launches, 1 x 4096 x 32/4 heads x 128, causal): 0x00 554 us, 0x55 592 us, 0xB5 612 us, 0xFF 636 us: none is the default.
+#define AB_POLY_MASK 0x00u
 #endif
 
 struct AttnBwdArgs {
@@ -345,8 +347,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
           const float4 ls = *reinterpret_cast<const float4*>(st_lse + u * 4);
-          // five of every eight exponentials on the FMA pipe (polynomial), three on the special-function unit: the
-          // latter's rate, not the arithmetic, bounds this phase otherwise
+          // AB_POLY_MASK chooses, element by element, the polynomial (FMA pipe) or the special-function unit
           const float x0 = fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x);
           const float x1 = fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y);
           const float x2 = fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z);

@@ -33,6 +33,8 @@ struct GemmArgs {
   int mode;
   int num_groups;
   const int* offs;      // [num_groups + 1] row offsets (device memory)
+  const int* offs2;     // kgroup only, optional: offsets of a second (A, B) operand pair whose rows are reduced into
+                        // the same outputs in the same launch (two micro-batches share one pass over the gradient)
   int b_group_rows;     // rows of the B tensor map that belong to one group
   void* D;
   long long ldd;
@@ -53,6 +55,7 @@ struct TileInfo {
   int am, ak;  // A tile origin: M coordinate, K coordinate base
   int bn, bk;  // B tile origin: N coordinate, K coordinate base
   int num_kb, last_steps;
+  int k2, num_kb2, last_steps2;  // second operand pair of a kgroup launch: K base, k-blocks (0 = none), last block's steps
   int row0, row_end, col0;
   long long d_off;
 };
@@ -79,6 +82,7 @@ struct Scheduler {
       int mt = first_m + local % gsz, nt = local / gsz;
       ti.am = mt * BM; ti.ak = 0; ti.bn = nt * BN; ti.bk = 0;
       ti.num_kb = (a.K + BK - 1) / BK; ti.last_steps = BK / UMMA_K;
+      ti.k2 = 0; ti.num_kb2 = 0; ti.last_steps2 = 0;
       ti.row0 = mt * BM; ti.row_end = a.M; ti.col0 = nt * BN; ti.d_off = 0;
       t += stride;
       return true;
@@ -86,9 +90,11 @@ struct Scheduler {
     while (g < a.num_groups) {
       int r0 = a.offs[g], r1 = a.offs[g + 1];
       int rows = r1 - r0;
+      int q0 = 0, rows2 = 0;
+      if (a.mode == GEMM_KGROUP && a.offs2) { q0 = a.offs2[g]; rows2 = a.offs2[g + 1] - q0; }
       int tiles;
       if (a.mode == GEMM_MGROUP) tiles = ((rows + BM - 1) / BM) * n_tiles;
-      else tiles = rows > 0 ? m_tiles * n_tiles : 0;
+      else tiles = (rows + rows2) > 0 ? m_tiles * n_tiles : 0;
       if (t < g_base + tiles) {
         int local = t - g_base;
         int mt = local / n_tiles, nt = local - mt * n_tiles;
@@ -98,6 +104,7 @@ struct Scheduler {
           // B origin carries the group: K-major B adds rows to N, MN-major B adds rows to K.
           ti.bn += 0; ti.bk += 0;
           ti.num_kb = (a.K + BK - 1) / BK; ti.last_steps = BK / UMMA_K;
+          ti.k2 = 0; ti.num_kb2 = 0; ti.last_steps2 = 0;
           ti.row0 = r0 + mt * BM; ti.row_end = r1; ti.col0 = nt * BN; ti.d_off = 0;
           ti.d_off = (long long)g;  // reused below as group index
         } else {
@@ -106,6 +113,10 @@ struct Scheduler {
           ti.num_kb = (rows + BK - 1) / BK;
           int rem = rows - (ti.num_kb - 1) * BK;
           ti.last_steps = (rem + UMMA_K - 1) / UMMA_K;
+          ti.k2 = q0;
+          ti.num_kb2 = (rows2 + BK - 1) / BK;
+          int rem2 = rows2 - (ti.num_kb2 - 1) * BK;
+          ti.last_steps2 = (rem2 + UMMA_K - 1) / UMMA_K;
           ti.row0 = mt * BM; ti.row_end = a.M; ti.col0 = nt * BN;
           ti.d_off = (long long)g;
         }
@@ -125,7 +136,8 @@ struct Scheduler {
 template <int BN, bool A_MN, bool B_MN, bool A_GATHER, bool DEEP_EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmD, const GemmArgs args) {
+                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmA2,
+                 const __grid_constant__ CUtensorMap tmB2, const GemmArgs args) {
   constexpr int B_TILE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
   constexpr int STAGES = DEEP_EPI ? 3 : ((BN == 256) ? 4 : 6);
@@ -236,7 +248,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (args.mode == GEMM_MGROUP) {
           if (B_MN) bk += grp * args.b_group_rows; else bn += grp * args.b_group_rows;
         }
-        for (int kb = 0; kb < ti.num_kb; ++kb, ++it) {
+        const int total_kb = ti.num_kb + ti.num_kb2;
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
           int s = it % STAGES;
           uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, args.err, PT_ERR_TIMEOUT_PRODUCER);
@@ -244,20 +257,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full[s], STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
-          int kk = kb * BK;
+          // the second operand pair of a kgroup launch continues the reduction of the same tile
+          const bool second = kb >= ti.num_kb;
+          const CUtensorMap* mA = second ? &tmA2 : &tmA;
+          const CUtensorMap* mB = second ? &tmB2 : &tmB;
+          const int ka = second ? ti.k2 + (kb - ti.num_kb) * BK : ti.ak + kb * BK;
+          const int kbB = second ? ti.k2 + (kb - ti.num_kb) * BK : bk + kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, &full[s], ti.ak + kk, ti.am);
+            tma_load_2d(sa, mA, &full[s], ka, ti.am);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sa + j * (BK * 128), &tmA, &full[s], ti.am + 64 * j, ti.ak + kk);
+              tma_load_2d(sa + j * (BK * 128), mA, &full[s], ti.am + 64 * j, ka);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, &full[s], bk + kk, bn);
+            tma_load_2d(sb, mB, &full[s], kbB, bn);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (BK * 128), &tmB, &full[s], bn + 64 * j, bk + kk);
+              tma_load_2d(sb + j * (BK * 128), mB, &full[s], bn + 64 * j, kbB);
           }
         }
       }
@@ -292,7 +310,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < ti.num_kb; ++kb, ++it) {
+        const int total_kb = ti.num_kb + ti.num_kb2;
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
           int s = it % STAGES;
           uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait_bounded(&full[s], ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
@@ -300,7 +319,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after();
           uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           uint32_t b_addr = a_addr + A_TILE_BYTES;
-          int steps = (kb == ti.num_kb - 1) ? ti.last_steps : (BK / UMMA_K);
+          int steps = (kb == ti.num_kb - 1) ? ti.last_steps : (kb == total_kb - 1 && ti.num_kb2 > 0) ? ti.last_steps2 : (BK / UMMA_K);
           for (int k = 0; k < steps; ++k) {
             uint64_t ad = A_MN ? make_smem_desc_sw128(a_addr + k * 2048, BK * 128, 1024)
                                : make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
@@ -562,7 +581,8 @@ constexpr int gemm_smem_bytes() {
 
 template <int BN, bool A_MN, bool B_MN, bool A_GATHER = false, bool DEEP_EPI = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
-                const GemmArgs& args, int grid, cudaStream_t stream) {
+                const GemmArgs& args, int grid, cudaStream_t stream, const CUtensorMap* tmA2 = nullptr,
+                const CUtensorMap* tmB2 = nullptr) {
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, A_GATHER, DEEP_EPI>;
   constexpr int smem = gemm_smem_bytes<BN, DEEP_EPI>();
   static bool configured = false;
@@ -571,7 +591,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, 192, smem, stream>>>(tmA, tmB, tmD, args);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmB, tmD, tmA2 ? *tmA2 : tmA, tmB2 ? *tmB2 : tmB, args);
   return (int)cudaGetLastError();
 }
 
@@ -631,7 +651,7 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
   }
   GemmArgs args;
   args.M = M; args.N = N; args.K = K; args.mode = mode; args.num_groups = num_groups;
-  args.offs = offs; args.b_group_rows = b_group_rows; args.D = D; args.ldd = ldd;
+  args.offs = offs; args.offs2 = nullptr; args.b_group_rows = b_group_rows; args.D = D; args.ldd = ldd;
   args.d_group_stride = d_group_stride; args.out_fp32 = out_fp32; args.accumulate = accumulate;
   args.use_tma_store = tma_store_ok ? 1 : 0;
   args.epi = epi;
@@ -669,4 +689,39 @@ PT_API int pt_gemm_bf16(const void* A, const void* B, void* D, int mode, int M, 
     case 7: return launch_gemm<256, true, true>(tmA, tmB, tmD, args, grid, stream);
   }
   return -1;
+}
+
+// Expert weight gradients of two micro-batches in one launch: for every group g,
+//   D_g += A1[offs1[g]:offs1[g+1]]^T B1[...] + A2[offs2[g]:offs2[g+1]]^T B2[...]
+// (A* [R*, M], B* [R*, N] bf16 row-major, read MN-major; D [G, M, N] bf16 or fp32, accumulated with TMA reduce-add).
+// One pass over the gradient buffer instead of two: the launch is bound by that read-modify-write, not by its FLOPs.
+// Group sizes must be multiples of 16 in both operand pairs.
+PT_API int pt_gemm_bf16_kgroup2(const void* A1, const void* B1, const int* offs1, long long rows1, const void* A2,
+                                const void* B2, const int* offs2, long long rows2, void* D, int M, int N, long long lda,
+                                long long ldb, long long ldd, long long d_group_stride, int num_groups, int out_fp32,
+                                void* stream_) {
+  using namespace pt;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || num_groups <= 0) return 0;
+  if (N % 8 != 0 || rows1 <= 0 || rows2 <= 0) return -2;
+  const int bn = (N >= 256) ? 256 : 128;
+  CUtensorMap tmA, tmB, tmA2, tmB2, tmD;
+  if (encode_tmap_2d(&tmA, A1, TM_BF16, rows1, M, lda, BK, 64, TM_SW_128)) return 1001;
+  if (encode_tmap_2d(&tmB, B1, TM_BF16, rows1, N, ldb, BK, 64, TM_SW_128)) return 2001;
+  if (encode_tmap_2d(&tmA2, A2, TM_BF16, rows2, M, lda, BK, 64, TM_SW_128)) return 1002;
+  if (encode_tmap_2d(&tmB2, B2, TM_BF16, rows2, N, ldb, BK, 64, TM_SW_128)) return 2002;
+  if (encode_tmap_3d(&tmD, D, out_fp32 ? TM_F32 : TM_BF16, num_groups, M, N, ldd, d_group_stride, 1, 32, out_fp32 ? 32 : 64,
+                     TM_SW_128))
+    return 3001;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = 0; args.mode = GEMM_KGROUP; args.num_groups = num_groups;
+  args.offs = offs1; args.offs2 = offs2; args.b_group_rows = 0; args.D = D; args.ldd = ldd;
+  args.d_group_stride = d_group_stride; args.out_fp32 = out_fp32; args.accumulate = 1;
+  args.use_tma_store = 0;
+  args.epi = 2;
+  args.err = device_status_word();
+  args.a_idx = nullptr; args.a_idx_div = 1; args.a_idx_len = 0;
+  const int grid = sm_count();
+  return bn == 256 ? launch_gemm<256, true, true, false, true>(tmA, tmB, tmD, args, grid, stream, &tmA2, &tmB2)
+                   : launch_gemm<128, true, true, false, true>(tmA, tmB, tmD, args, grid, stream, &tmA2, &tmB2);
 }

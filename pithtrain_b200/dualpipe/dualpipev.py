@@ -30,6 +30,7 @@ from . import comm
 from .execution import ChunkRecord, ExecutionCtx, model_backward, model_forward, nvtx_range
 from .overlap import overlapped_forward_backward
 from .schedule import Action, backward_dst, backward_src, build_schedule, forward_dst, forward_src
+from ..ops.moe import flush_pending_expert_wgrads
 from .utils import FP8WeightCacheControl, WeightGradStore, scatter
 
 
@@ -329,6 +330,7 @@ class DualPipeV(nn.Module):
         for action in build_schedule(self.pp_size, self.pp_rank, num_chunks):
             self._run(action)
         assert not WeightGradStore.funcs_queue, "deferred weight gradients left in the queue"
+        flush_pending_expert_wgrads()
         self._commit_and_wait_comm()
 
         loss, outputs = None, None

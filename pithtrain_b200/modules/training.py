@@ -146,6 +146,9 @@ class TrainingCfg(SlottedDefault):
     ``reference``: expert gradients are averaged over dp x cp only, so they are ``ep`` times larger than in a run
     without expert parallelism — what FSDP2's per-mesh averaging gives the reference
     (pithtrain/modules/training.py:341-342); use it to reproduce the reference's loss curves at ``ep > 1``."""
+    pair_expert_wgrads: bool = False
+    """Compute the expert weight gradients of two consecutive micro-batches in one launch per weight: halves the
+    passes over the expert gradient buffers; holds one extra micro-batch of expert activations per layer."""
     num_hidden_layers_override: Optional[int] = None
     """Truncate the model (tests and smoke runs only)."""
     pipeline_overlap: bool = True
@@ -370,6 +373,9 @@ def setup_training(cfg: object) -> None:
     if torch.cuda.is_available():
         torch.cuda.manual_seed_all(t.seed)
     setup_model(t, cfg.distributed)
+    from ..ops import moe as _moe
+
+    _moe.PAIR_EXPERT_WGRADS = bool(t.pair_expert_wgrads)
     training.optimizers = t.optimizer(t)
     training.schedulers = t.scheduler(t)
     from ..tools.memory_trace import attach_from_env

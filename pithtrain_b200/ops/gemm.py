@@ -231,3 +231,24 @@ def grouped_gemm_tn(dy: torch.Tensor, x: torch.Tensor, offs: torch.Tensor, out: 
     _launch(dy, x, out, KGROUP, N, K, 0, True, True, (R, N), dy.stride(0), (R, K), x.stride(0),
             N, K, offs=offs, num_groups=G, d_group_stride=N * K, accumulate=True)
     return out
+
+
+@torch.no_grad()
+def grouped_gemm_tn_pair(dy1: torch.Tensor, x1: torch.Tensor, offs1: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor,
+                         offs2: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[g] += dy1[rows1_g].T @ x1[rows1_g] + dy2[rows2_g].T @ x2[rows2_g]``: the expert weight gradients of two
+    micro-batches in one launch. The launch is bound by the read-modify-write of ``out`` (the whole ``[G, N, K]``
+    gradient buffer), not by its FLOPs, so one pass for two micro-batches nearly halves its cost."""
+    G, N, K = out.shape
+    if not (_native_ok(dy1, x1) and _native_ok(dy2, x2)) or N % 8 != 0 or K % 8 != 0:
+        grouped_gemm_tn(dy1, x1, offs1, out, accumulate=True)
+        return grouped_gemm_tn(dy2, x2, offs2, out, accumulate=True)
+    for t, n in ((dy1, "dy1"), (x1, "x1"), (dy2, "dy2"), (x2, "x2")):
+        _chk2d(t, n)
+    assert out.is_contiguous() and offs1.dtype == torch.int32 and offs2.dtype == torch.int32
+    assert dy1.stride(0) == dy2.stride(0) and x1.stride(0) == x2.stride(0)
+    rc = _native.lib().pt_gemm_bf16_kgroup2(dy1.data_ptr(), x1.data_ptr(), offs1.data_ptr(), dy1.shape[0], dy2.data_ptr(),
+                                            x2.data_ptr(), offs2.data_ptr(), dy2.shape[0], out.data_ptr(), N, K, dy1.stride(0),
+                                            x1.stride(0), K, N * K, G, int(out.dtype == torch.float32), _native.stream_ptr())
+    _native.check(rc, "pt_gemm_bf16_kgroup2")
+    return out

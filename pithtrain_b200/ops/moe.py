@@ -260,6 +260,36 @@ def rows_group_id(offs: torch.Tensor, R: int) -> torch.Tensor:
 GATHER_IN_GEMM = False
 
 
+# Weight gradients of an expert block are produced for two micro-batches at a time (one K-grouped launch per weight
+# with two operand pairs): a launch reads and rewrites the whole [experts, out, in] gradient buffer, which costs more
+# than its FLOPs, so halving the number of passes is worth holding one micro-batch's operands until the next arrives.
+# ``flush_pending_expert_wgrads`` (called at the end of every step, before gradients are reduced) runs what is left.
+# Off by default: it keeps dY / act / dGU of one extra micro-batch per layer alive; ``TrainingCfg.pair_expert_wgrads``.
+PAIR_EXPERT_WGRADS = False
+_PENDING_WGRAD: dict = {}
+
+
+def _run_expert_wgrad(ew: "ExpertWeights", k: int, a, b) -> None:
+    dyg, act_s, dgu, x, slot_of_row, offs, n_rows = a
+    xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
+    if b is None:
+        G.grouped_gemm_tn(dyg, act_s, offs, ew.g2(), accumulate=True)
+        G.grouped_gemm_tn(dgu, xs, offs, ew.g1(), accumulate=True)
+        return
+    dyg2, act2, dgu2, x2, sor2, offs2, n2 = b
+    xs2 = gather_rows(x2, sor2, div=k, n_rows=n2)
+    G.grouped_gemm_tn_pair(dyg, act_s, offs, dyg2, act2, offs2, ew.g2())
+    G.grouped_gemm_tn_pair(dgu, xs, offs, dgu2, xs2, offs2, ew.g1())
+
+
+def flush_pending_expert_wgrads() -> None:
+    """Run the weight gradients of micro-batches that found no partner (odd counts, end of the step)."""
+    with torch.no_grad():
+        while _PENDING_WGRAD:
+            _, (ew, k, mine) = _PENDING_WGRAD.popitem()
+            _run_expert_wgrad(ew, k, mine, None)
+
+
 class ExpertWeights:
     """What :func:`moe_experts` needs from the owning module.
 
@@ -371,9 +401,16 @@ class _MoEExpertsFn(torch.autograd.Function):
         del dxs
 
         def wgrad_fn(dyg=dyg, act_s=act_s, dgu=dgu, x=x, slot_of_row=slot_of_row, offs=offs, n_rows=n_rows):
-            G.grouped_gemm_tn(dyg, act_s, offs, ew.g2(), accumulate=True)
-            xs = gather_rows(x, slot_of_row, div=k, n_rows=n_rows)
-            G.grouped_gemm_tn(dgu, xs, offs, ew.g1(), accumulate=True)
+            mine = (dyg, act_s, dgu, x, slot_of_row, offs, n_rows)
+            if PAIR_EXPERT_WGRADS and use_native(dyg):
+                other = _PENDING_WGRAD.pop(id(ew), None)
+                if other is None:
+                    # wait for the next micro-batch of this expert block: both share one pass over the gradients
+                    _PENDING_WGRAD[id(ew)] = (ew, k, mine)
+                    return
+                _run_expert_wgrad(ew, k, other[2], mine)
+            else:
+                _run_expert_wgrad(ew, k, mine, None)
 
         if WeightGradStore.enabled:
             WeightGradStore.put(wgrad_fn)

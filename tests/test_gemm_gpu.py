@@ -138,6 +138,28 @@ def test_grouped_tn(sizes, N, K, acc_epilogue):
     assert calc_diff(outb.float(), refb) < 1e-4
 
 
+@pytest.mark.parametrize("sizes1,sizes2", [([128, 256], [64, 16]), ([16, 0, 48, 304], [0, 32, 0, 16]),
+                                           ([208] * 8, [1024, 0, 16, 0, 640, 0, 272, 48]), ([0, 0, 64], [0, 0, 0])])
+@pytest.mark.parametrize("N,K", [(256, 128), (768, 2048), (192, 320)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grouped_tn_pair(sizes1, sizes2, N, K, dtype):
+    """Two micro-batches' weight gradients in one launch equal the fp32 sum of both products."""
+    o1, o2 = _offsets(sizes1), _offsets(sizes2)
+    Gn = len(sizes1)
+    dy1, x1 = _rand(int(o1[-1]) + 64, N), _rand(int(o1[-1]) + 64, K)
+    dy2, x2 = _rand(int(o2[-1]) + 16, N), _rand(int(o2[-1]) + 16, K)
+    out = torch.randn(Gn, N, K, device="cuda").to(dtype)
+    ref = out.float().clone()
+    G.grouped_gemm_tn_pair(dy1, x1, o1, dy2, x2, o2, out)
+    _native.check_status()
+    for g in range(Gn):
+        a, b = int(o1[g]), int(o1[g + 1])
+        ref[g] += dy1[a:b].float().t() @ x1[a:b].float()
+        a, b = int(o2[g]), int(o2[g + 1])
+        ref[g] += dy2[a:b].float().t() @ x2[a:b].float()
+    assert calc_diff(out.float(), ref) < (1e-5 if dtype == torch.float32 else 1e-4)
+
+
 @pytest.mark.parametrize("sizes,N,K", [([256, 0, 128, 400, 16], 512, 256), ([1008, 48, 640], 1536, 2048)])
 def test_grouped_gather_matches_explicit_gather(sizes, N, K):
     """The in-kernel TMA row gather equals gather_rows followed by the plain grouped GEMM, bit for bit."""
