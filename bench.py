@@ -124,8 +124,9 @@ def main() -> int:
                     help="N=1 only: GiB of Muon momentum kept on the device, the rest streams from pinned host memory")
     ap.add_argument("--state-dtype", choices=["auto", "fp32", "bf16"], default="auto",
                     help="gradient accumulators and Muon momentum: auto = fp32 from 2 GPUs on (the reference's precision), bf16 on one GPU")
-    ap.add_argument("--pair-wgrads", choices=["auto", "on", "off"], default="auto",
-                    help="expert weight gradients of two micro-batches per launch (auto: from 2 GPUs on, where fp32 accumulators make the pass over them costly)")
+    ap.add_argument("--pair-wgrads", action="store_true",
+                    help="expert weight gradients of two micro-batches per launch (TrainingCfg.pair_expert_wgrads); off: with worst-case "
+                         "sized expert-parallel buffers the operands held for the partner micro-batch do not fit at this batch size")
     ap.add_argument("--fp8", action="store_true", help="not the headline run: forward/dgrad GEMMs in block-scaled e4m3 (dtype says so)")
     ap.add_argument("--ep-backend", default=os.environ.get("PITH_EP_BACKEND", "auto"))
     ap.add_argument("--routing", choices=["natural", "balanced"], default="natural",
@@ -179,7 +180,7 @@ def main() -> int:
     t.muon_momentum_dtype = "fp32" if mom_wide else "bf16"
     t.offload_optimizer_state = (n == 1)  # the 30B model + gradients fill one 180 GB GPU
     t.optimizer_device_state_gb = args.resident_state_gb if n == 1 else 0.0  # spare HBM keeps part of it resident
-    t.pair_expert_wgrads = (n >= 2) if args.pair_wgrads == "auto" else args.pair_wgrads == "on"
+    t.pair_expert_wgrads = bool(args.pair_wgrads)
     t.num_hidden_layers_override = args.layers
     t.benchmark = args.routing == "balanced"
 

@@ -403,10 +403,13 @@ class _MoEExpertsFn(torch.autograd.Function):
         def wgrad_fn(dyg=dyg, act_s=act_s, dgu=dgu, x=x, slot_of_row=slot_of_row, offs=offs, n_rows=n_rows):
             mine = (dyg, act_s, dgu, x, slot_of_row, offs, n_rows)
             if PAIR_EXPERT_WGRADS and use_native(dyg):
-                other = _PENDING_WGRAD.pop(id(ew), None)
+                # an expert block is known by its down projection's storage: the owning module builds a new
+                # ExpertWeights view on every call
+                key = ew.w2.data_ptr()
+                other = _PENDING_WGRAD.pop(key, None)
                 if other is None:
                     # wait for the next micro-batch of this expert block: both share one pass over the gradients
-                    _PENDING_WGRAD[id(ew)] = (ew, k, mine)
+                    _PENDING_WGRAD[key] = (ew, k, mine)
                     return
                 _run_expert_wgrad(ew, k, other[2], mine)
             else:

@@ -204,6 +204,41 @@ def test_moe_experts_vs_loop():
     assert calc_diff(g2, w2r.grad) < 1e-3
 
 
+def test_moe_expert_wgrads_paired_across_micro_batches(monkeypatch):
+    """With pairing on, three micro-batches (one pair + one flushed leftover) give the gradients of the unpaired path."""
+    torch.manual_seed(16)
+    k, E, H, I = 4, 8, 256, 128
+    w1 = bf(E, 2 * I, H, scale=0.05)
+    w2 = bf(E, H, I, scale=0.05)
+    batches = []
+    for n in (640, 333, 512):
+        eids = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(n)]).int()
+        eids[::5, 1] = -1
+        batches.append((bf(n, H), torch.rand(n, k, device="cuda"), eids, bf(n, H)))
+
+    def run(paired):
+        monkeypatch.setattr(M, "PAIR_EXPERT_WGRADS", paired)
+        g1, g2 = torch.zeros_like(w1, dtype=torch.float32), torch.zeros_like(w2, dtype=torch.float32)
+        dxs = []
+        for x, w, eids, go in batches:
+            x = x.clone().requires_grad_()
+            ew = M.ExpertWeights(w1, w2, lambda: g1, lambda: g2)  # a new view per call, as the owning module makes
+            M.moe_experts(x, w.clone().requires_grad_(), eids, ew).backward(go)
+            dxs.append(x.grad)
+        if paired:
+            assert len(M._PENDING_WGRAD) == 1
+        M.flush_pending_expert_wgrads()
+        assert not M._PENDING_WGRAD
+        _native.check_status()
+        return g1, g2, dxs
+
+    a1, a2, adx = run(False)
+    b1, b2, bdx = run(True)
+    assert calc_diff(a1, b1) < 1e-6 and calc_diff(a2, b2) < 1e-6
+    for p, q in zip(adx, bdx):
+        assert torch.equal(p, q)
+
+
 @pytest.mark.parametrize("n,k,E,valid", [(2048, 8, 128, 1000), (700, 4, 16, 699), (64, 2, 8, 0)])
 def test_route_sort_device_side_count(n, k, E, valid):
     """Slots at or past a device-side count are ignored (the fused EP transport sizes by capacity)."""
