@@ -62,15 +62,15 @@ struct AttnFwdCfg {
 };
 
 
-// p = 2^(s * scale - m) for the 128 scores of a row (in registers), written back over the scores' TMEM columns as
-// packed bf16 (chunk c of 32 keys -> columns [16c, 16c+16)); returns the row sum. POLY selects which of every 8
+// p = 2^(s * scale - m) for chunks [C0, C1) of the 128 scores of a row (in registers; a chunk = 32 keys), written back
+// over the scores' TMEM columns as packed bf16 (chunk c -> columns [16c, 16c+16)); returns their sum. POLY selects which of every 8
 // element pairs are evaluated by polynomial on the FMA pipe instead of the special-function unit.
-template <uint32_t POLY>
+template <uint32_t POLY, int C0, int C1>
 __device__ __forceinline__ float softmax_exp_store(const uint32_t (&sv)[128], float scale_log2, float m_use, uint32_t tS) {
   float l4[4] = {0.f, 0.f, 0.f, 0.f};
   const float nm = -m_use;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = C0; c < C1; ++c) {
     uint32_t w[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -105,9 +105,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* v_full = bars + 9;             // KST
   uint64_t* v_empty = bars + 13;           // KST
   uint64_t* s_full = bars + 17;            // NQ  MMA -> softmax
-  uint64_t* p_full = bars + 19;            // NQ  softmax (4 warps) -> MMA
+  uint64_t* p_full = bars + 19;            // NQ  softmax (4 warps) -> MMA: keys 0..63 of P are in TMEM
   uint64_t* o_done = bars + 21;            // NQ  MMA -> softmax: last P V of the tile finished
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 23);
+  uint64_t* turn = bars + 23;              // NQ  issuer -> the other issuer: "my block is issued, yours may follow"
+  uint64_t* p_full2 = bars + 25;           // NQ  softmax (4 warps) -> MMA: keys 64..127 of P are in TMEM
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 27);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,7 +147,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], NQ);   // every MMA warp releases a stage
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], NQ);
     }
-    for (int t = 0; t < NQ; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
+    for (int t = 0; t < NQ; ++t) {
+      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&p_full2[t], 4); mbar_init(&o_done[t], 1);
+      mbar_init(&turn[t], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -218,8 +223,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------------------------------------------------------- MMA issuers, one warp (one thread) per query tile
     // A thread that issues tcgen05.mma runs nearly in lock step with the tensor core (the queue behind it is short), so
     // every barrier wait, fence and commit of a lone issuer is tensor-core idle time. With one issuer per tile the MMAs
-    // of one tile run while the other issuer does its bookkeeping. The tiles are independent; the K / V stages are
-    // released when both issuers have committed past them.
+    // of one tile run while the other issuer does its bookkeeping. The K / V stages are released when both issuers
+    // have committed past them.
+    // The issuers take turns, block by block (a block = P V of step j and S of step j+1 of one tile): tile 0, tile 1,
+    // tile 0, ... Left alone, both tiles fall into the same phase (their softmax warps share the special-function
+    // unit, finish together and hand both blocks to the tensor core at once), and then the tensor core idles through
+    // every softmax and the softmax warps through every block: measured 5700 cycles per step of the pair, where the
+    // MMAs take 2048. With the turns the softmax of one tile runs under the other tile's block.
     const int t = warp - 1;
     if (lane == 0 && J1 > J0) {
       constexpr uint32_t IDESC_S = make_idesc(1, 1, 128, 128, false, false);
@@ -258,6 +268,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = step_S(J0);
       for (int j = J0; j < J1 && ok; ++j) {
         const int c = j - J0, s = c % KST;
+        if (NQ == 2) {
+          // tile 0 opens step c once tile 1 has issued its block of step c-1; tile 1 follows tile 0 within the step
+          if (t == 1) ok = mbar_wait_bounded(&turn[1], c & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          else if (c > 0) ok = mbar_wait_bounded(&turn[0], (c - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+        }
         ok = mbar_wait_bounded(&v_full[s], (c / KST) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
         if (!ok) break;
         if (j >= lo && j < hi) {
@@ -266,13 +282,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_after();
           const uint32_t b_lo = v_lo0 + s * (Cfg::V_BYTES >> 4);
           const uint32_t acc0 = (j != lo) ? 1u : 0u;
+          // the softmax warps hand P over in two halves of 64 keys: the first half's MMAs run under the second's exponentials
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
+          for (int k = 0; k < 4; ++k)
             umma_f16_ts_lh(tO, tS + k * 8, b_lo + ((k * 2048) >> 4), HI, IDESC_O, k != 0 ? 1u : acc0);
+          ok = mbar_wait_bounded(&p_full2[t], (j - lo) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 4; k < 8; ++k)
+            umma_f16_ts_lh(tO, tS + k * 8, b_lo + ((k * 2048) >> 4), HI, IDESC_O, 1u);
           if (j == hi - 1) umma_commit(&o_done[t]);
         }
         release(&v_empty[s]);
         if (j + 1 < J1) ok = step_S(j + 1);
+        if (NQ == 2) mbar_arrive(&turn[1 - t]);
       }
     }
   } else if (warp >= 4) {
@@ -300,24 +324,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { ok = false; break; }
       tc_fence_after();
+      // The scores arrive in four chunks of 32 keys; the row maximum of a chunk is taken while the next chunk loads
+      // (four independent chains: a thread has little other work to hide a 128-long dependency).
       uint32_t sv[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
-      tmem_ld_wait();
       const int kpos0 = j * 128;
       const bool masked = kpos0 < lo_row || kpos0 + 127 > hi_row;
-      if (masked) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (kpos0 + i < lo_row || kpos0 + i > hi_row) sv[i] = 0xff800000u;  // -inf
-      }
-      // row maximum: four independent chains (a thread has little other work to hide a 128-long dependency)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      tmem_ld_32x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
 #pragma unroll
-      for (int i = 0; i < 128; i += 8) {
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld_32x32(tS + (c + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * (c + 1)]));
+        if (masked) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1])));
+          for (int i = 32 * c; i < 32 * c + 32; ++i)
+            if (kpos0 + i < lo_row || kpos0 + i > hi_row) sv[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 32 * c; i < 32 * c + 32; i += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1])));
+        }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * args.scale_log2);  // scale > 0
@@ -344,12 +372,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // masked tiles need exact zeros, which only the special-function path gives; the others put a share of the
       // exponentials on the FMA pipe
       // (the choice is made per warp: the TMEM stores inside are warp-collective)
-      if (__any_sync(0xffffffffu, masked)) l += softmax_exp_store<0u>(sv, args.scale_log2, m_use, tS);
-      else l += softmax_exp_store<AT_POLY_MASK>(sv, args.scale_log2, m_use, tS);
+      const bool any_masked = __any_sync(0xffffffffu, masked);
+      if (any_masked) l += softmax_exp_store<0u, 0, 2>(sv, args.scale_log2, m_use, tS);
+      else l += softmax_exp_store<AT_POLY_MASK, 0, 2>(sv, args.scale_log2, m_use, tS);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
+      if (any_masked) l += softmax_exp_store<0u, 2, 4>(sv, args.scale_log2, m_use, tS);
+      else l += softmax_exp_store<AT_POLY_MASK, 2, 4>(sv, args.scale_log2, m_use, tS);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full2[t]);
     }
     if (ok) {
       int good = 1;
