@@ -28,6 +28,9 @@ namespace pt {
 
 constexpr int AT_SLAB = 128 * 64 * 2;      // one [128 x 64] bf16 swizzle slab: 16 KB
 constexpr float AT_RESCALE_LOG2 = 8.0f;    // tolerated growth of a row maximum before O is rescaled
+#ifndef AT_ROLLED
+#define AT_ROLLED 0  // 1: softmax passes as rolled loops over 32-key chunks re-read from TMEM (measured 196 us against 189 us)
+#endif
 #ifndef AT_POLY_MASK
 // Which of every 8 scores take the polynomial exp2 on the FMA pipe instead of the special-function unit (bit i =
 // element i mod 8). Measured at 1 x 4096 x 32/4 heads x 128, causal: 0x00 210 us, 0x55 216 us, 0xB5 223 us, 0x77 233 us,
@@ -324,6 +327,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { ok = false; break; }
       tc_fence_after();
+#if AT_ROLLED
+      // Both passes over the 128 scores of the row (maximum, then exponentials) walk four chunks of 32 keys with the
+      // chunk loop kept rolled and read each chunk from TMEM when they need it: the straight-line form of this loop
+      // body is several times larger, and every instruction of it is fetched once per key tile.
+      const int kpos0 = j * 128;
+      const bool masked = kpos0 < lo_row || kpos0 + 127 > hi_row;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32];
+        tmem_ld_32x32(tS + c * 32, sv);
+        tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kpos0 + 32 * c + i < lo_row || kpos0 + 32 * c + i > hi_row) sv[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1])));
+        }
+      }
+#else
       // The scores arrive in four chunks of 32 keys; the row maximum of a chunk is taken while the next chunk loads
       // (four independent chains: a thread has little other work to hide a 128-long dependency).
       uint32_t sv[128];
@@ -347,6 +375,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1])));
         }
       }
+#endif
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * args.scale_log2);  // scale > 0
       // The S MMA of this step was issued after the P V MMA of the previous one, so O is stable here.
@@ -372,6 +401,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // masked tiles need exact zeros, which only the special-function path gives; the others put a share of the
       // exponentials on the FMA pipe
       // (the choice is made per warp: the TMEM stores inside are warp-collective)
+#if AT_ROLLED
+      {
+        const float nm = -m_use;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32], w[16];
+          tmem_ld_32x32(tS + c * 32, sv);
+          tmem_ld_wait();
+          if (masked) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kpos0 + 32 * c + i < lo_row || kpos0 + 32 * c + i > hi_row) sv[i] = 0xff800000u;  // -inf
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(sv[2 * i]), args.scale_log2, nm));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), args.scale_log2, nm));
+            l4[(2 * i) & 3] += e0;
+            l4[(2 * i + 1) & 3] += e1;
+            w[i] = pack_bf16x2(e0, e1);
+          }
+          // P chunk c -> columns [16c, 16c+16): the scores that were there belong to chunks already read
+          tmem_st_32x16(tS + c * 16, w);
+          if (c == 1) {
+            // first 64 keys of P are complete: their P V MMAs may start under the other half's exponentials
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[t]);
+          }
+        }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+      }
+#else
       const bool any_masked = __any_sync(0xffffffffu, masked);
       if (any_masked) l += softmax_exp_store<0u, 0, 2>(sv, args.scale_log2, m_use, tS);
       else l += softmax_exp_store<AT_POLY_MASK, 0, 2>(sv, args.scale_log2, m_use, tS);
@@ -384,6 +451,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
+#endif
       if (lane == 0) mbar_arrive(&p_full2[t]);
     }
     if (ok) {

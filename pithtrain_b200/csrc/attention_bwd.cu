@@ -23,12 +23,17 @@
 //
 // Every wait is bounded (mbar_wait_bounded); on a timeout the roles leave their loops, the CTA frees its TMEM and
 // the status word carries the code.
+#include <type_traits>
+
 #include "host_common.h"
 #include "ptx.cuh"
 
 namespace pt {
 
 constexpr int AB_SLAB = 128 * 64 * 2;  // one [128 x 64] bf16 swizzle slab: 16 KB
+#ifndef AB_EXP_CHUNK
+#define AB_EXP_CHUNK 32  // query columns per pass of the rolled exponential loop (32 or 16; measured 447 / 469 us)
+#endif
 #ifndef AB_POLY_MASK
 // Which of every 8 exponentials take the polynomial on the FMA pipe (see exp2_poly). Measured (all five backward
 // launches, 1 x 4096 x 32/4 heads x 128, causal): 0x00 554 us, 0x55 592 us, 0xB5 612 us, 0xFF 636 us: none is the default.
@@ -92,7 +97,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* dq_full = bars + 12;   // MMA -> reduce warps
   uint64_t* dq_read = bars + 13;   // reduce (4 warps) -> MMA: dQ has left TMEM
   uint64_t* all_done = bars + 14;  // MMA -> reduce warps: dK / dV complete
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* dk_done = bars + 15;   // MMA -> compute: the dK product of a step has read dS^T (its tile may be rewritten)
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +138,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(do_full, 1); mbar_init(do_empty, 2);
     mbar_init(s_full, 1); mbar_init(dp_full, 1);
     mbar_init(p_ready, 8); mbar_init(dp_read, 8); mbar_init(ds_ready, 8);
-    mbar_init(dq_full, 1); mbar_init(dq_read, 4); mbar_init(all_done, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_read, 4); mbar_init(all_done, 1); mbar_init(dk_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
@@ -290,16 +296,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ok = mbar_wait_bounded(ds_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
+          // dQ first: reading it out and handing its TMEM region to the next dP^T is the longest dependency of a step
+          // (dS -> dQ -> read-out -> dP^T -> dS), dK only accumulates
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_f16_lh(tRS, ds_m + ((k * 2048) >> 4), HI, k_m + ((k * 2048) >> 4), HI, IDESC_DQ, k != 0 ? 1u : 0u);
+          umma_commit(dq_full);
 #pragma unroll
           for (int g = 0; g < 2; ++g)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               umma_f16_lh(tDK, ds_k + ((g * AB_SLAB + k * 32) >> 4), HI, q_m + (((g * 4 + k) * 2048) >> 4), HI, IDESC_DK,
                           (g | k) != 0 ? 1u : accn);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_f16_lh(tRS, ds_m + ((k * 2048) >> 4), HI, k_m + ((k * 2048) >> 4), HI, IDESC_DQ, k != 0 ? 1u : 0u);
-          umma_commit(dq_full);
+          umma_commit(dk_done);
           umma_commit(&q_empty[n & 1]);
         }
         if (ok) umma_commit(all_done);
@@ -338,62 +347,80 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const float* st_lse = reinterpret_cast<const float*>(sStat + (n & 1) * 1024) + g * 64;
       const float* st_del = st_lse + 128;
-      uint32_t pk[32];  // P^T of my row, 64 query columns, packed bf16
-      {
-        uint32_t sv[64];
-        tmem_ld_32x32(tRS, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-        tmem_ld_32x32(tRS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-        tmem_ld_wait();
+      // Both phases below walk my 64 query columns in two chunks of 32 with the chunk loop kept rolled: fully unrolled,
+      // the loop body of a compute warp was ~30 KB of straight-line code, every instruction used once per query tile,
+      // and instruction fetch (not a pipe) bounded the warps ("no instruction" was their largest stall reason).
+      // P^T chunk c (AB_EXP_CHUNK / 2 packed columns) goes to the columns of my S^T half right after chunk c-1's: the
+      // scores there have been read by then.
+      // one rolled loop per case: the element masks (diagonal and ragged tiles only) stay out of the common loop
+      auto exp_pass = [&](auto masked_c) {
+        constexpr bool MASKED = decltype(masked_c)::value;
+#pragma unroll 1
+        for (int c = 0; c < 64 / AB_EXP_CHUNK; ++c) {
+          uint32_t sv[AB_EXP_CHUNK], pk[AB_EXP_CHUNK / 2];
+          if (AB_EXP_CHUNK == 32) tmem_ld_32x32(tRS + AB_EXP_CHUNK * c, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+          else tmem_ld_32x16(tRS + AB_EXP_CHUNK * c, *reinterpret_cast<uint32_t(*)[16]>(&sv[0]));
+          tmem_ld_wait();
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float4 ls = *reinterpret_cast<const float4*>(st_lse + u * 4);
-          // AB_POLY_MASK chooses, element by element, the polynomial (FMA pipe) or the special-function unit
-          const float x0 = fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x);
-          const float x1 = fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y);
-          const float x2 = fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z);
-          const float x3 = fmaf(__uint_as_float(sv[4 * u + 3]), args.scale_log2, -ls.w);
-          float p0 = (AB_POLY_MASK & (1u << ((4 * u + 0) & 7))) ? exp2_poly(x0) : ex2_approx(x0);
-          float p1 = (AB_POLY_MASK & (1u << ((4 * u + 1) & 7))) ? exp2_poly(x1) : ex2_approx(x1);
-          float p2 = (AB_POLY_MASK & (1u << ((4 * u + 2) & 7))) ? exp2_poly(x2) : ex2_approx(x2);
-          float p3 = (AB_POLY_MASK & (1u << ((4 * u + 3) & 7))) ? exp2_poly(x3) : ex2_approx(x3);
-          if (need_mask) {
-            const int qr = q0 + 4 * u;
-            const float pv[4] = {p0, p1, p2, p3};
-            float po[4];
+          for (int u = 0; u < AB_EXP_CHUNK / 4; ++u) {
+            const float4 ls = *reinterpret_cast<const float4*>(st_lse + c * AB_EXP_CHUNK + u * 4);
+            // AB_POLY_MASK chooses, element by element, the polynomial (FMA pipe) or the special-function unit
+            const float x0 = fmaf(__uint_as_float(sv[4 * u + 0]), args.scale_log2, -ls.x);
+            const float x1 = fmaf(__uint_as_float(sv[4 * u + 1]), args.scale_log2, -ls.y);
+            const float x2 = fmaf(__uint_as_float(sv[4 * u + 2]), args.scale_log2, -ls.z);
+            const float x3 = fmaf(__uint_as_float(sv[4 * u + 3]), args.scale_log2, -ls.w);
+            float p0 = (AB_POLY_MASK & (1u << ((4 * u + 0) & 7))) ? exp2_poly(x0) : ex2_approx(x0);
+            float p1 = (AB_POLY_MASK & (1u << ((4 * u + 1) & 7))) ? exp2_poly(x1) : ex2_approx(x1);
+            float p2 = (AB_POLY_MASK & (1u << ((4 * u + 2) & 7))) ? exp2_poly(x2) : ex2_approx(x2);
+            float p3 = (AB_POLY_MASK & (1u << ((4 * u + 3) & 7))) ? exp2_poly(x3) : ex2_approx(x3);
+            if (MASKED) {
+              const int qr = q0 + c * AB_EXP_CHUNK + 4 * u;
+              const float pv[4] = {p0, p1, p2, p3};
+              float po[4];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              bool vis = key_valid && qr + x < args.Sq;
-              if (args.causal) vis = vis && kp <= args.q_off + qr + x;
-              if (args.row_lo && vis) vis = kp >= args.row_lo[row_base + qr + x];
-              po[x] = vis ? pv[x] : 0.f;
+              for (int x = 0; x < 4; ++x) {
+                bool vis = key_valid && qr + x < args.Sq;
+                if (args.causal) vis = vis && kp <= args.q_off + qr + x;
+                if (args.row_lo && vis) vis = kp >= args.row_lo[row_base + qr + x];
+                po[x] = vis ? pv[x] : 0.f;
+              }
+              p0 = po[0]; p1 = po[1]; p2 = po[2]; p3 = po[3];
             }
-            p0 = po[0]; p1 = po[1]; p2 = po[2]; p3 = po[3];
+            pk[2 * u] = pack_bf16x2(p0, p1);
+            pk[2 * u + 1] = pack_bf16x2(p2, p3);
           }
-          pk[2 * u] = pack_bf16x2(p0, p1);
-          pk[2 * u + 1] = pack_bf16x2(p2, p3);
+          if (AB_EXP_CHUNK == 32) tmem_st_32x16(tRS + (AB_EXP_CHUNK / 2) * c, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+          else tmem_st_32x8(tRS + (AB_EXP_CHUNK / 2) * c, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
         }
-      }
-      // both column halves of my row have been read: P^T may overwrite the first 32 columns of my S^T half
-      tmem_st_32x32(tRS, pk);
+      };
+      if (need_mask) exp_pass(std::true_type{});
+      else exp_pass(std::false_type{});
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
 
-      if (lane == 0) good = mbar_wait_bounded(dp_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+      if (lane == 0) {
+        good = mbar_wait_bounded(dp_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+        // the previous step's dK product (issued after its dQ) must have finished reading the dS^T tile written below
+        if (good && n > 0) good = mbar_wait_bounded(dk_done, (n - 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;
+      }
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) break;
       tc_fence_after();
+      // dS^T = P^T o (dP^T - delta): P^T (as rounded for the dV product) is read back from TMEM, where it stays until
+      // the dQ product of this step overwrites the region (issued only after every compute warp has arrived below)
       {
-        uint32_t dp[64];
+        uint32_t dp[64], pk[32];
         tmem_ld_32x32(tRP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
         tmem_ld_32x32(tRP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+        tmem_ld_32x32(tRS, pk);
         tmem_ld_wait();
         // dP^T has left TMEM: the next S^T may be issued into this region
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(dp_read);
-        // 64 query columns = 8 chunks of 16 bytes in my 128-byte row of the dS^T tile
+        // 64 query columns = 8 chunks of 16 bytes in my 128-byte row of the dS^T tile (this part is short: unrolled)
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
           const float4 da = *reinterpret_cast<const float4*>(st_del + t * 8);
