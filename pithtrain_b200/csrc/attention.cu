@@ -170,6 +170,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // 12 warps share the register file three to a scheduler (168 each). The softmax threads hold a whole score row and
     // need independent exponentials in flight; the producer, the issuers and the idle warp need few registers.
     // Each role's code follows its own setmaxnreg so that the compiler may use the larger budget there.
+    // setmaxnreg moves registers within what the CTA received at launch (384 threads x 168 as compiled): a request
+    // beyond that pool would wait for ever
+    static_assert(NQ != 2 || 128 * 72 + 256 * 216 <= 384 * 168, "setmaxnreg budget exceeds the launch allocation");
     if (warp < 4) setmaxnreg_dec<72>();
   }
 

@@ -156,6 +156,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // 16 warps share the register file four to a scheduler (128 each): the producer and the issuers need few, the
   // compute and reduction threads hold 64..128 values at a time. Each role's code follows its own setmaxnreg so that
   // the compiler may use the larger budget there.
+  // (setmaxnreg moves registers within what the CTA received at launch, 512 threads x 128: the sum below must fit)
+  static_assert(128 * 56 + 384 * 152 <= 512 * 128, "setmaxnreg budget exceeds the launch allocation");
   if (warp < 4) setmaxnreg_dec<56>();
 
   if (warp == 0) {
