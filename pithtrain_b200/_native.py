@@ -62,6 +62,7 @@ SIGS = {
     "pt_set_peer_wait_limit_ns": "L",
     "pt_gemm_bf16": "PPPIIIIIILLLLLLLLPIILIIIIIIPILP",
     "pt_gemm_bf16_kgroup2": "PPPLPPPLPIILLLLIIP",
+    "pt_merge_partial": "PPPIPPIIIILP",
     "pt_rmsnorm_fwd": "PPPPPPIIFIP",
     "pt_rmsnorm_bwd_grid": "I",
     "pt_rmsnorm_bwd": "PPPPPPPIIIP",
@@ -142,7 +143,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 # Number of kernel launches issued through this module since it was last reset (bench bookkeeping).
 LAUNCHES = 0
-_LAUNCHES_PER_CALL = {"pt_route_sort": 4, "pt_attn_bwd": 5}
+_LAUNCHES_PER_CALL = {"pt_route_sort": 4, "pt_attn_bwd": 5, "pt_merge_partial": 2}
 
 
 def check(rc: int, what: str) -> None:

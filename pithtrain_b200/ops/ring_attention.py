@@ -118,16 +118,40 @@ def block_bwd(do, q, k, v, out, lse, scale: float, causal: bool = False, q_off: 
     return dq, dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)
 
 
-def merge_partial(out: Optional[torch.Tensor], lse: Optional[torch.Tensor], o_p: torch.Tensor, lse_p: torch.Tensor):
-    """Fold a partial ``(o_p, lse_p)`` into the running ``(out, lse)`` (all fp32)."""
-    o_p = o_p.float()
-    if out is None:
-        return o_p, lse_p
+def merge_partial_math(out: torch.Tensor, lse: torch.Tensor, o_p: torch.Tensor, lse_p: torch.Tensor):
+    """Tensor-op restatement of the merge (fp32): the CPU path and the oracle of the kernel."""
     new = torch.logaddexp(lse, lse_p)
     safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)
     w_old = torch.exp(lse - safe).permute(0, 2, 1).unsqueeze(-1)
     w_new = torch.exp(lse_p - safe).permute(0, 2, 1).unsqueeze(-1)
-    return out * w_old + o_p * w_new, new
+    return out * w_old + o_p.float() * w_new, new
+
+
+MERGE_KERNEL = True  # GPU: one pass of csrc/merge.cu instead of the eight tensor ops of merge_partial_math
+
+
+def merge_partial(out: Optional[torch.Tensor], lse: Optional[torch.Tensor], o_p: torch.Tensor, lse_p: torch.Tensor):
+    """Fold a partial ``(o_p [B, S, H, D], lse_p [B, H, S])`` into the running fp32 ``(out, lse)``.
+
+    The running ``out`` is updated in place on the kernel path (it is a private accumulator of the ring loop).
+    Counterpart in the reference: the ``combine_partial`` step of pithtrain/operators/ring_attention.py.
+    """
+    if out is None:
+        return o_p.float(), lse_p
+    B, S, H, D = o_p.shape
+    if (MERGE_KERNEL and out.is_cuda and out.dtype == torch.float32 and out.is_contiguous() and lse.is_contiguous()
+            and lse_p.is_contiguous() and lse.dtype == torch.float32 and lse_p.dtype == torch.float32
+            and o_p.dtype in (torch.bfloat16, torch.float32) and D % 4 == 0 and o_p.stride(3) == 1
+            and o_p.stride(2) == D and o_p.stride(0) == S * o_p.stride(1) and o_p.stride(1) % 4 == 0
+            and o_p.data_ptr() % 16 == 0):
+        from .. import _native
+
+        new = torch.empty_like(lse)
+        rc = _native.lib().pt_merge_partial(out.data_ptr(), lse.data_ptr(), o_p.data_ptr(), int(o_p.dtype == torch.float32),
+                                            lse_p.data_ptr(), new.data_ptr(), B, S, H, D, o_p.stride(1), _native.stream_ptr())
+        _native.check(rc, "pt_merge_partial")
+        return out, new
+    return merge_partial_math(out, lse, o_p, lse_p)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -458,3 +458,31 @@ def test_gated_delta_rule_recurrence_kernels(B, S, H, dk, dv):
     got = GD.gated_delta_rule(q, k, v, g, beta)
     ref = GD.gated_delta_rule_recurrent(q, k, v, g, beta)
     assert calc_diff(got.float(), ref.float()) < 1e-3
+
+
+@pytest.mark.parametrize("B,S,H,D,dtype", [(1, 256, 8, 128, torch.bfloat16), (2, 96, 4, 64, torch.float32),
+                                           (1, 40, 3, 192, torch.bfloat16)])
+def test_merge_partial_kernel_vs_math(B, S, H, D, dtype):
+    """The ring-attention merge kernel equals its fp32 tensor restatement, rows without any key so far included."""
+    from pithtrain_b200.ops import ring_attention as R
+
+    torch.manual_seed(21)
+    out = torch.randn(B, S, H, D, device="cuda")
+    lse = torch.randn(B, H, S, device="cuda") * 3
+    # the partial as a slice of a wider buffer (row pitch larger than H * D), as the fused projections produce it
+    wide = torch.randn(B, S, H * D + 64, device="cuda").to(dtype)
+    o_p = wide[..., :H * D].view(B, S, H, D)
+    lse_p = torch.randn(B, H, S, device="cuda") * 3
+    lse[:, 0, :7] = float("-inf")            # nothing seen before
+    lse_p[:, 1, 3:9] = float("-inf")         # nothing in this block
+    lse[:, 2, 5] = float("-inf"); lse_p[:, 2, 5] = float("-inf")  # nothing at all
+    out[:, :7, 0] = 0.0
+    out[:, 5, 2] = 0.0
+    ref_out, ref_lse = R.merge_partial_math(out.clone(), lse.clone(), o_p, lse_p)
+    got_out, got_lse = R.merge_partial(out.clone(), lse.clone(), o_p, lse_p)
+    _native.check_status()
+    assert torch.equal(torch.isinf(got_lse), torch.isinf(ref_lse))
+    fin = ~torch.isinf(ref_lse)
+    assert (got_lse[fin] - ref_lse[fin]).abs().max() < 1e-4
+    assert calc_diff(got_out, ref_out) < 1e-6
+    assert float(got_out[:, 5, 2].abs().max()) == 0.0
