@@ -91,14 +91,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* do_empty = bars + 6;   // 1
   uint64_t* s_full = bars + 7;     // MMA -> compute
   uint64_t* dp_full = bars + 8;    // MMA -> compute
-  uint64_t* p_ready = bars + 9;    // compute (8 warps) -> MMA: P^T is in TMEM
+  uint64_t* p_ready = bars + 9;    // compute (8 warps) -> MMA: P^T is in TMEM; steps alternate between this barrier and
+                                   // p_ready2 (the compute warps reach the next step's arrival without any help from the
+                                   // back issuer, so a single barrier could come round before that thread has looked)
   uint64_t* dp_read = bars + 10;   // compute (8 warps) -> MMA: dP^T has left TMEM
   uint64_t* ds_ready = bars + 11;  // compute (8 warps) -> MMA: dS^T is in shared memory
   uint64_t* dq_full = bars + 12;   // MMA -> reduce warps
   uint64_t* dq_read = bars + 13;   // reduce (4 warps) -> MMA: dQ has left TMEM
   uint64_t* all_done = bars + 14;  // MMA -> reduce warps: dK / dV complete
   uint64_t* dk_done = bars + 15;   // MMA -> compute: the dK product of a step has read dS^T (its tile may be rewritten)
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_ready2 = bars + 16;  // odd steps' P^T barrier
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,7 +140,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2); }  // both issuers release
     mbar_init(do_full, 1); mbar_init(do_empty, 2);
     mbar_init(s_full, 1); mbar_init(dp_full, 1);
-    mbar_init(p_ready, 8); mbar_init(dp_read, 8); mbar_init(ds_ready, 8);
+    mbar_init(p_ready, 8); mbar_init(p_ready2, 8); mbar_init(dp_read, 8); mbar_init(ds_ready, 8);
     mbar_init(dq_full, 1); mbar_init(dq_read, 4); mbar_init(all_done, 1); mbar_init(dk_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -285,7 +288,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // dV += P^T dO  (P^T packed bf16 in TMEM: query columns 0..63 at +0, 64..127 at +64)
           ok = mbar_wait_bounded(do_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
-          ok = mbar_wait_bounded(p_ready, ph, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
+          ok = mbar_wait_bounded((n & 1) ? p_ready2 : p_ready, (n >> 1) & 1, abort_flag, args.err, PT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -400,7 +403,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive((n & 1) ? p_ready2 : p_ready);
 
       if (lane == 0) {
         good = mbar_wait_bounded(dp_full, ph, abort_flag, args.err, PT_ERR_TIMEOUT_EPILOGUE) ? 1 : 0;

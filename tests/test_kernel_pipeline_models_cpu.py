@@ -1,70 +1,18 @@
-"""Interleaving checks of the mbarrier pipelines of ``csrc/attention.cu`` (producer warp, MMA thread, tensor pipe,
-softmax warps) and ``csrc/gemm_2cta.cu`` (two CTAs: producers, leader MMA thread, tensor pipe, epilogues), restated step
-by step with the kernels' barrier names, arrival counts and wait parities.
+"""Interleaving check of the mbarrier protocol of ``csrc/gemm_2cta.cu`` (two CTAs: producers, leader MMA thread, tensor
+pipe, epilogues), restated step by step with the kernel's barrier names, arrival counts and wait parities. (The
+attention forward kernel has its own model in ``tests/test_attention_pipeline_model_cpu.py``.)
 
 An mbarrier is modelled by its arrival count: phase ``p`` has completed once ``count * (p + 1)`` arrivals happened, and
-``wait(parity)`` passes when the current (incomplete) phase has the other parity — which is also what makes a waiter
+``wait(parity)`` passes when the current (incomplete) phase has the other parity, which is also what makes a waiter
 that falls two phases behind see the wrong phase, so the model exposes that mistake too. ``tcgen05.commit`` arrivals are
 asynchronous: they happen when a separate "tensor pipe" agent completes the batch, any time after it was issued.
 The checker walks every reachable interleaving and asserts that no agent is stuck and that every buffer is used in
-order: K/V stages are not reloaded before the MMAs that read them completed, S buffers are not overwritten before the
-softmax has read them, P is not rewritten before the previous PV completed, O is only touched between PV batches.
-Mutations (a wrong parity, a missing wait) must be caught.
+order. Mutations (a missing commit to the peer, a wrong arrival count) must be caught.
 """
 from collections import deque
 from typing import Dict, List, Tuple
 
 import pytest
-
-KSTAGES = 2
-
-
-def build(n_kv: int, *, s_empty_parity_flip: bool = True, wait_pv_before_p: bool = True, k_empty_commit: bool = True):
-    """Step lists of the four agents for one CTA that walks ``n_kv`` key tiles."""
-    prod: List[Tuple] = [("arrive", "q_full")]
-    for j in range(n_kv):
-        s, ph = j % KSTAGES, (j // KSTAGES) & 1
-        prod += [("wait", f"k_empty{s}", ph ^ 1), ("check_free", "K", j), ("mark", f"K_loaded{j}"), ("arrive", f"k_full{s}"),
-                 ("wait", f"v_empty{s}", ph ^ 1), ("check_free", "V", j), ("mark", f"V_loaded{j}"), ("arrive", f"v_full{s}")]
-
-    mma: List[Tuple] = [("wait", "q_full", 0)]
-    pipe: List[Tuple] = []
-
-    def issue_s(j):
-        s, sb = j % KSTAGES, j & 1
-        par = ((j >> 1) & 1) ^ (1 if s_empty_parity_flip else 0)
-        mma.extend([("wait", f"s_empty{sb}", par), ("wait", f"k_full{s}", (j // KSTAGES) & 1),
-                    ("need", f"K_loaded{j}"), ("check_s_free", j), ("issue", f"S{j}")])
-        arrives = ([f"k_empty{s}"] if k_empty_commit else []) + [f"s_full{sb}"]
-        pipe.append(("complete", f"S{j}", arrives))
-
-    issue_s(0)
-    for j in range(n_kv):
-        if j + 1 < n_kv:
-            issue_s(j + 1)
-        s = j % KSTAGES
-        mma.extend([("wait", "p_full", j & 1), ("wait", f"v_full{s}", (j // KSTAGES) & 1), ("need", f"P_written{j}"),
-                    ("need", f"V_loaded{j}"), ("issue", f"PV{j}")])
-        pipe.append(("complete", f"PV{j}", [f"v_empty{s}", "pv_done"]))
-
-    soft: List[Tuple] = []
-    for j in range(n_kv):
-        sb = j & 1
-        # pass 1 reads S for the row maximum; the buffer is handed back only at the end of pass 2, which comes after
-        # the wait for the previous PV (the kernel's order)
-        soft += [("wait", f"s_full{sb}", (j >> 1) & 1), ("need", f"done_S{j}")]
-        if j > 0 and wait_pv_before_p:
-            soft.append(("wait", "pv_done", (j - 1) & 1))
-        if j > 0:
-            soft += [("need", f"done_PV{j - 1}"), ("forbid", f"issued_PV{j}")]  # O rescale and P rewrite window
-        soft += [("mark", f"S_read{j}"), ("arrive", f"s_empty{sb}"), ("mark", f"P_written{j}"), ("arrive", "p_full")]
-    soft += [("wait", "pv_done", (n_kv - 1) & 1), ("need", f"done_PV{n_kv - 1}"), ("mark", "O_read")]
-    return {"prod": prod, "mma": mma, "pipe": pipe, "soft": soft}
-
-
-COUNTS = {"q_full": 1, "p_full": 1, "pv_done": 1, **{f"{b}{s}": 1 for b in ("k_full", "k_empty", "v_full", "v_empty", "s_full", "s_empty")
-                                                        for s in range(2)}}
-
 
 class Stuck(Exception):
     pass
@@ -74,14 +22,10 @@ class Hazard(Exception):
     pass
 
 
-def explore(n_kv: int, **mutation) -> int:
-    return explore_agents(build(n_kv, **mutation), COUNTS)
-
-
 def explore_agents(agents, counts, issuer: str = "mma") -> int:
     """Walk every interleaving of the agents' step lists. Step kinds: ``wait`` (barrier, parity), ``arrive`` (barrier),
     ``issue`` (batch) by the ``issuer``, ``complete`` (batch, barriers) by a pipe agent once the batch was issued,
-    ``mark`` (fact), ``need`` / ``forbid`` (fact) and the stage / buffer checks of the attention model."""
+    ``mark`` (fact), ``need`` / ``forbid`` (fact)."""
     names = list(agents)
     steps = [agents[n] for n in names]
     issue_index = {st[1]: i for i, st in enumerate(agents[issuer]) if st[0] == "issue"}
@@ -128,15 +72,6 @@ def explore_agents(agents, counts, issuer: str = "mma") -> int:
             elif kind == "forbid":
                 if st[1] in marks:
                     raise Hazard(f"{a} runs while {st[1]} at {pcs}")
-            elif kind == "check_free":  # a K/V stage is reloaded for tile j: the MMAs of tile j - KSTAGES must be complete
-                what, j = st[1], st[2]
-                prev = j - KSTAGES
-                if prev >= 0 and ("done_S%d" % prev if what == "K" else "done_PV%d" % prev) not in marks:
-                    raise Hazard(f"{what} stage of tile {prev} reloaded for tile {j} before its MMAs completed")
-            elif kind == "check_s_free":  # the S buffer of tile j was last used by tile j - 2
-                j = st[1]
-                if j >= 2 and f"S_read{j - 2}" not in marks:
-                    raise Hazard(f"S buffer of tile {j - 2} overwritten by tile {j} before the softmax read it")
             moved = True
             nxt = pcs[:i] + (pcs[i] + 1,) + pcs[i + 1:]
             if nxt not in seen:
@@ -145,27 +80,6 @@ def explore_agents(agents, counts, issuer: str = "mma") -> int:
         if not moved and any(pcs[i] < len(steps[i]) for i in range(len(names))):
             raise Stuck(f"no agent can move at {dict(zip(names, pcs))}")
     return len(seen)
-
-
-@pytest.mark.parametrize("n_kv", [1, 2, 3, 5, 6])
-def test_attention_pipeline_has_no_deadlock_and_no_buffer_hazard(n_kv):
-    assert explore(n_kv) > 10
-
-
-def test_wrong_first_wait_parity_on_the_s_buffers_deadlocks():
-    # waiting for parity 0 on a fresh "empty" barrier blocks for ever: the kernel must start with parity 1
-    with pytest.raises(Stuck):
-        explore(3, s_empty_parity_flip=False)
-
-
-def test_rewriting_p_without_waiting_for_the_previous_pv_is_a_hazard():
-    with pytest.raises(Hazard):
-        explore(3, wait_pv_before_p=False)
-
-
-def test_k_stage_must_be_released_by_a_commit():
-    with pytest.raises(Stuck):
-        explore(4, k_empty_commit=False)
 
 
 # ------------------------------------------------------------------------------------------------ 2-CTA GEMM
