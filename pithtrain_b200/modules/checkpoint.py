@@ -291,8 +291,16 @@ def _sched_state(s) -> Dict[str, Any]:
 
 
 def build_save_state(model: nn.Module, optimizers, schedulers) -> Dict[str, Any]:
-    """The ``{"app": ...}`` tree for this rank (tensors moved to the CPU)."""
-    model_state = {k: v.detach().cpu() for k, v in to_canonical_model(dict(model.state_dict()), model).items()}
+    """The ``{"app": ...}`` tree for this rank (tensors moved to the CPU).
+
+    Every model tensor is staged by exactly one of the ranks that hold a replica of it: dense tensors are replicated over
+    dp x cp x ep, expert tensors over dp x cp, and only the first rank of each replica set copies its tensors to the host
+    and hands them to the writer. (Without this every rank of a data-parallel job would stage a full replica, tens of GB
+    per rank, for the planner to discard all but one.) Optimizer state exists on its owner only and needs no filter.
+    """
+    first_replica = distributed.dp_rank == 0 and distributed.cp_rank == 0
+    model_state = {k: v.detach().cpu() for k, v in to_canonical_model(dict(model.state_dict()), model).items()
+                   if first_replica and (".experts." in k or distributed.ep_rank == 0)}
     optim = to_canonical_optim(optimizers, model)
     optim["state"] = {fqn: {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in st.items()}
                       for fqn, st in optim["state"].items()}

@@ -58,6 +58,14 @@ def run(rank, world, pp, ep, save_location, phase, model="qwen3"):
         for _ in range(2):
             train_step(cfg)
         save_training_checkpoint(cfg)
+        from pithtrain_b200.contexts import distributed as d
+        from pithtrain_b200.modules.checkpoint import build_save_state
+
+        staged = build_save_state(training.model, training.optimizers, training.schedulers)["app"]["model"]
+        if d.dp_rank > 0:
+            assert not staged, "a data-parallel replica staged model tensors"
+        elif d.ep_rank > 0:
+            assert staged and all(".experts." in k for k in staged), "a dense tensor was staged by more than one rank"
         st = full_state(training.model)
         opt = to_canonical_optim(training.optimizers, training.model)["state"]
         torch.save({"model": st, "optim": {k: {f: (v.clone() if torch.is_tensor(v) else v) for f, v in e.items()} for k, e in opt.items()}},

@@ -24,6 +24,13 @@ def test_reshard_roundtrip(tmp_path, save_layout, load_layout):
     launch(pp1 * ep1, checkpoint_worker.run, pp1, ep1, str(tmp_path), "load")
 
 
+def test_data_parallel_replicas_stage_nothing(tmp_path):
+    """Saved at dp2 x ep2 (only the first replica stages model tensors, dense ones only on its first ep rank), loaded at
+    dp1 x ep2: every tensor is there exactly once."""
+    launch(4, checkpoint_worker.run, 1, 2, str(tmp_path), "save")
+    launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")
+
+
 @pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
 def test_muon_state_roundtrip_other_families(tmp_path, model):
     """Muon momentum and AdamW moments of the MLA / shared-expert / dense-first-layer model and of the model with
