@@ -298,6 +298,8 @@ def build_save_state(model: nn.Module, optimizers, schedulers) -> Dict[str, Any]
     and hands them to the writer. (Without this every rank of a data-parallel job would stage a full replica, tens of GB
     per rank, for the planner to discard all but one.) Optimizer state exists on its owner only and needs no filter.
     """
+    for g in training.shard_groups:
+        g.ensure_params()  # parameters released by DistributedCfg.reshard_params are gathered again (a collective)
     first_replica = distributed.dp_rank == 0 and distributed.cp_rank == 0
     model_state = {k: v.detach().cpu() for k, v in to_canonical_model(dict(model.state_dict()), model).items()
                    if first_replica and (".experts." in k or distributed.ep_rank == 0)}

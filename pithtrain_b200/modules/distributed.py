@@ -32,6 +32,11 @@ class DistributedCfg(SlottedDefault):
     expert_parallel_size: int = 1
     timeout: timedelta = timedelta(minutes=15)
     sharding_strategy: Literal["fsdp", "hsdp"] = "fsdp"
+    reshard_params: bool = False
+    """Shard the parameters too between steps: after the gradient reduction a rank keeps only the parameters it owns
+    and the next step starts with one all-gather per shard group (the reference's FSDP2 setting, where resharding is
+    switched off inside a pipeline step). Off by default: with 180 GB per GPU the parameters stay resident and the
+    updated regions are published by peer stores. Uses the NCCL shard collectives."""
     backend: str = "auto"
     """"auto" picks nccl when CUDA is available and gloo otherwise."""
     ep_backend: Literal["auto", "nccl", "fused"] = "auto"

@@ -261,7 +261,7 @@ def materialize_small_params(model: nn.Module) -> None:
 
 
 def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dtype: torch.dtype = torch.float32,
-               expert_grad_divisor: Optional[int] = None):
+               expert_grad_divisor: Optional[int] = None, reshard_params: bool = False):
     """Place the parameters of both chunks into flat shard groups (experts over dp×cp, the rest over
     dp×cp×ep). ``hsdp`` shards inside cp(×ep) and replicates over dp. ``expert_grad_divisor`` (default ``ep``)
     divides the expert gradients on top of the shard-group average; 1 reproduces the reference's scaling."""
@@ -285,7 +285,7 @@ def apply_fsdp(modules: nn.Sequential, sharding_strategy: str = "fsdp", grad_dty
         else:
             raise ValueError(f"Unknown sharding_strategy: {sharding_strategy!r}")
         groups.extend(build_shard_groups(m, grad_dtype=grad_dtype, prefix=f"module.{i}.", device=d.device,
-                                         expert_grad_divisor=expert_grad_divisor, **kw))
+                                         expert_grad_divisor=expert_grad_divisor, reshard_params=reshard_params, **kw))
     training.shard_groups = tuple(groups)
     return modules
 
@@ -326,7 +326,8 @@ def setup_model(cfg: TrainingCfg, distributed_cfg: Any) -> None:
     modules = nn.Sequential(*modules)
     gdt = torch.float32 if cfg.grad_dtype == "fp32" else torch.bfloat16
     apply_fsdp(modules, getattr(distributed_cfg, "sharding_strategy", "fsdp"), gdt,
-               expert_grad_divisor=1 if cfg.expert_grad_scaling == "reference" else None)
+               expert_grad_divisor=1 if cfg.expert_grad_scaling == "reference" else None,
+               reshard_params=bool(getattr(distributed_cfg, "reshard_params", False)))
     for m in modules:
         materialize_small_params(m)
         init_weights(m, config.num_hidden_layers, cfg.init_std, cfg.depth_scaled_init, seed=cfg.seed,

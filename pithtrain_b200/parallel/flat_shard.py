@@ -13,7 +13,10 @@ per optimizer step (pithtrain/modules/training.py:328-376, pithtrain/dualpipe/du
   reduced gradients of its parameters (one ``reduce_scatter`` over the flat buffer), runs the
   optimizer for them — Muon's Newton-Schulz sees full matrices without any gather — and the updated
   regions are all-gathered back into every rank's flat parameter buffer;
-* optimizer state exists only on the owner, so it is sharded like ZeRO-1/2/3 state.
+* optimizer state exists only on the owner, so it is sharded like ZeRO-1/2/3 state;
+* with ``reshard_params`` the parameters are sharded too between steps: after the gradient reduction a rank frees the
+  regions it does not own (optimizer step, checkpoint staging and anything else between steps then run with
+  ``1/group_size`` of the group's parameters resident) and the next step starts with one all-gather.
 
 Expert parameters shard over dp×cp, everything else over dp×cp×ep, like the reference's FSDP meshes.
 """
@@ -83,8 +86,15 @@ class FlatShardGroup:
     def __init__(self, name: str, named_params: Sequence[Tuple[str, nn.Parameter]], fusions: Sequence[FusedWeights],
                  group=None, group_size: int = 1, group_rank: int = 0, grad_dtype: torch.dtype = torch.float32,
                  replica_group=None, replica_size: int = 1, device=None, param_swapper=None,
-                 fused_collectives: bool = True) -> None:
+                 fused_collectives: bool = True, reshard_params: bool = False) -> None:
         self.name = name
+        # reshard_params: between the gradient reduction of one step and the start of the next, a rank keeps only the
+        # parameters it owns; the regions of the other owners are freed and gathered again when the next step (or a
+        # checkpoint save) needs them. That is parameter sharding in the form the reference runs it: FSDP2 with
+        # resharding switched off inside a pipeline step, i.e. one gather per step
+        # (pithtrain/modules/training.py:328-376, pithtrain/dualpipe/dualpipev.py:513-525,629-653).
+        self.reshard_params = bool(reshard_params) and group_size > 1
+        self.own_param: Optional[torch.Tensor] = None
         self.group, self.group_size, self.group_rank = group, group_size, group_rank
         self.replica_group, self.replica_size = replica_group, replica_size
         self.grad_divisor = 1
@@ -111,7 +121,7 @@ class FlatShardGroup:
         total = self.region * group_size
         self.comm = None
         self._fused_sumsq = None
-        if fused_collectives and group_size > 1 and torch.device(device).type == "cuda":
+        if fused_collectives and not self.reshard_params and group_size > 1 and torch.device(device).type == "cuda":
             from . import fsdp_fused
 
             if fsdp_fused.usable(group, group_size, device):
@@ -124,6 +134,10 @@ class FlatShardGroup:
         else:
             self.flat_param = torch.zeros(total, dtype=self.param_dtype, device=device)
             self.flat_grad = torch.zeros(total, dtype=grad_dtype, device=device)
+        if self.reshard_params:
+            # owned parameters live in a buffer of their own, which persists; the flat buffer holds the others' regions
+            # (and, while allocated, a copy of this rank's) and can be released
+            self.own_param = torch.zeros(self.region, dtype=self.param_dtype, device=device)
         replaced: Dict[int, nn.Parameter] = {}
 
         def swap(old: nn.Parameter, new: nn.Parameter) -> None:
@@ -135,6 +149,9 @@ class FlatShardGroup:
             for u in self.units:
                 n = u.numel
                 pv, gv = self.flat_param[u.offset:u.offset + n], self.flat_grad[u.offset:u.offset + n]
+                if self.own_param is not None and u.owner == group_rank:
+                    lo = u.offset - group_rank * self.region
+                    pv = self.own_param[lo:lo + n]
                 if u.fused is not None:
                     u.fused.rebind(pv, gv, copy=True, swap=swap)
                     u.params = list(u.fused.params)
@@ -268,6 +285,20 @@ class FlatShardGroup:
             total += c.float().pow(2).sum()
         return total / self.replica_size
 
+    def params_resident(self) -> bool:
+        return self.flat_param is None or self.flat_param.untyped_storage().size() > 0
+
+    def release_params(self) -> None:
+        """Free the regions of the other owners (``reshard_params`` only; the owned parameters are elsewhere)."""
+        if self.reshard_params and self.flat_param is not None and self.params_resident():
+            self.flat_param.untyped_storage().resize_(0)
+
+    def ensure_params(self) -> None:
+        """Make every parameter of the group readable again after :meth:`release_params`."""
+        if self.reshard_params and self.flat_param is not None and not self.params_resident():
+            self.flat_param.untyped_storage().resize_(self.flat_param.numel() * self.flat_param.element_size())
+            self.gather_params()
+
     def gather_params(self) -> None:
         """Publish the owners' updated regions to every rank of the shard group."""
         if self.flat_param is None or self.group_size == 1:
@@ -275,7 +306,9 @@ class FlatShardGroup:
         if self.comm is not None:
             self.comm.push_params()
             return
-        mine = self.my_slice(self.flat_param)
+        if self.reshard_params and not self.params_resident():
+            return  # stays sharded; ensure_params gathers when the parameters are needed
+        mine = self.own_param if self.own_param is not None else self.my_slice(self.flat_param)
         backend = dist.get_backend(self.group)
         if backend == "nccl":
             dist.all_gather_into_tensor(self.flat_param, mine, group=self.group)
@@ -293,7 +326,8 @@ class FlatShardGroup:
     def nbytes(self) -> int:
         if self.flat_param is None:
             return 0
-        return self.flat_param.numel() * self.flat_param.element_size() + self.flat_grad.numel() * self.flat_grad.element_size()
+        own = 0 if self.own_param is None else self.own_param.numel() * self.own_param.element_size()
+        return own + self.flat_param.numel() * self.flat_param.element_size() + self.flat_grad.numel() * self.flat_grad.element_size()
 
 
 def find_fusions(module: nn.Module) -> List[FusedWeights]:
@@ -312,7 +346,8 @@ def is_expert_param(name: str) -> bool:
 def build_shard_groups(module: nn.Module, *, expert_group=None, expert_group_size: int = 1, expert_group_rank: int = 0,
                        dense_group=None, dense_group_size: int = 1, dense_group_rank: int = 0,
                        grad_dtype: torch.dtype = torch.float32, expert_replica=(None, 1), dense_replica=(None, 1),
-                       prefix: str = "", device=None, expert_grad_divisor: int = 1) -> List[FlatShardGroup]:
+                       prefix: str = "", device=None, expert_grad_divisor: int = 1,
+                       reshard_params: bool = False) -> List[FlatShardGroup]:
     """Create the two shard groups (experts, everything else) of one model chunk."""
     named = [(prefix + n, p) for n, p in module.named_parameters() if p.requires_grad]
     fusions = find_fusions(module)
@@ -336,10 +371,10 @@ def build_shard_groups(module: nn.Module, *, expert_group=None, expert_group_siz
     if de:
         groups.append(FlatShardGroup(prefix + "dense", de, de_f, dense_group, dense_group_size, dense_group_rank,
                                      grad_dtype, dense_replica[0], dense_replica[1], device=device,
-                                     param_swapper=param_swapper))
+                                     param_swapper=param_swapper, reshard_params=reshard_params))
     if ex:
         groups.append(FlatShardGroup(prefix + "experts", ex, ex_f, expert_group, expert_group_size, expert_group_rank,
                                      grad_dtype, expert_replica[0], expert_replica[1], device=device,
-                                     param_swapper=param_swapper))
+                                     param_swapper=param_swapper, reshard_params=reshard_params))
         groups[-1].grad_divisor = max(int(expert_grad_divisor), 1)
     return groups

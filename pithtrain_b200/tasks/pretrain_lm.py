@@ -152,6 +152,8 @@ def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], 
     t, d = cfg.training, distributed
     model, optimizers, schedulers = training.model, training.optimizers, training.schedulers
     model.train()
+    for g in training.shard_groups:
+        g.ensure_params()  # no-op unless DistributedCfg.reshard_params released them after the previous step
     assert t.global_batch_size % (t.micro_batch_size * d.dp_size * d.ep_size) == 0
     accumulate_steps = t.global_batch_size // (t.micro_batch_size * d.dp_size * d.ep_size)
 
@@ -178,6 +180,7 @@ def forward_backward_update(cfg: PretrainLMCfg, tokens: Optional[torch.Tensor], 
             g.fold_autograd_grads()
             g.scale_grads(scale)
             g.reduce_grads()
+            g.release_params()  # reshard_params: only the owned parameters stay through the optimizer step
     else:
         for p in model.parameters():
             if p.grad is not None:

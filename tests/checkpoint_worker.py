@@ -42,7 +42,7 @@ def full_state(model):
     return {k: v.detach().clone() for k, v in to_canonical_model(dict(model.state_dict()), model).items()}
 
 
-def run(rank, world, pp, ep, save_location, phase, model="qwen3"):
+def run(rank, world, pp, ep, save_location, phase, model="qwen3", reshard=False):
     from pithtrain_b200.contexts import training
     from pithtrain_b200.modules.checkpoint import load_training_checkpoint, save_training_checkpoint, to_canonical_optim
     from pithtrain_b200.modules.distributed import setup_distributed
@@ -51,6 +51,7 @@ def run(rank, world, pp, ep, save_location, phase, model="qwen3"):
     from pithtrain_b200.tasks.pretrain_lm import train_step
 
     cfg = make_cfg(pp, ep, save_location, 4, model)
+    cfg.distributed.reshard_params = bool(reshard)
     setup_logging(cfg)
     setup_distributed(cfg, failfast=False)
     setup_training(cfg)

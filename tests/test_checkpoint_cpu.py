@@ -31,6 +31,13 @@ def test_data_parallel_replicas_stage_nothing(tmp_path):
     launch(2, checkpoint_worker.run, 1, 2, str(tmp_path), "load")
 
 
+def test_checkpoint_with_parameters_sharded_between_steps(tmp_path):
+    """``reshard_params``: the save gathers the released parameter regions first, the load fills owned and foreign
+    parameters alike, and the resumed job (again with released parameters) keeps training."""
+    launch(4, checkpoint_worker.run, 1, 2, str(tmp_path), "save", "qwen3", True)
+    launch(4, checkpoint_worker.run, 1, 2, str(tmp_path), "load", "qwen3", True)
+
+
 @pytest.mark.parametrize("model", ["deepseek", "gpt_oss"])
 def test_muon_state_roundtrip_other_families(tmp_path, model):
     """Muon momentum and AdamW moments of the MLA / shared-expert / dense-first-layer model and of the model with

@@ -29,6 +29,7 @@ def baseline(tmp_path_factory):
     ("cp2", 2, 1, 1, 2, "fsdp"),
     ("dp2_ep2_hsdp", 4, 1, 2, 1, "hsdp"),
     ("pp2_cp2", 4, 2, 1, 2, "fsdp"),
+    ("dp2_ep2_resharded_params", 4, 1, 2, 1, "fsdp+reshard"),
 ])
 def test_mesh_matches_single_process(tmp_path, baseline, name, world, pp, ep, cp, strategy):
     got = _curve(tmp_path, name, world, pp, ep, cp, strategy)

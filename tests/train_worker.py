@@ -16,7 +16,8 @@ def run(rank: int, world: int, pp: int, ep: int, cp: int, strategy: str, out_pat
     cfg = PretrainLMCfg()
     d = cfg.distributed
     d.pipeline_parallel_size, d.expert_parallel_size, d.context_parallel_size = pp, ep, cp
-    d.sharding_strategy = strategy
+    d.sharding_strategy, _, extra = strategy.partition("+")
+    d.reshard_params = extra == "reshard"
     t = cfg.training
     t.model = dict(model_type="qwen3_moe", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                    rms_norm_eps=1e-6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
@@ -40,6 +41,11 @@ def run(rank: int, world: int, pp: int, ep: int, cp: int, strategy: str, out_pat
     for _ in range(steps):
         m = train_step(cfg)
         rows.append({"loss": m.get("loss"), "gradient_norm": m["gradient_norm"]})
+        if d.reshard_params:
+            # between steps a rank holds only the parameters it owns: the other owners' regions are freed
+            sharded = [g for g in training.shard_groups if g.group_size > 1]
+            assert sharded and all(g.reshard_params and not g.params_resident() for g in sharded)
+            assert all(g.own_param.numel() * g.group_size == g.flat_param.numel() for g in sharded)
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(rows, f)
