@@ -32,6 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--optimizer", choices=["muon", "adamw"], default="muon")
     ap.add_argument("--momentum-dtype", choices=["bf16", "fp32"], default="bf16")
     ap.add_argument("--offload-optimizer-state", action="store_true")
+    ap.add_argument("--reshard-params", action="store_true", help="DistributedCfg.reshard_params (parameters sharded between steps)")
     ap.add_argument("--resident-state-gb", type=float, default=0.0, help="with offload: GiB of optimizer state kept on the device")
     ap.add_argument("--ep-backend", choices=["fused", "nccl"], default="fused")
     ap.add_argument("--fp8-training", action="store_true", help="TrainingCfg.fp8: adds the cached e4m3 weight copies")
@@ -51,6 +52,7 @@ def main(argv=None) -> int:
                       global_batch_size=a.global_batch_size, sequence_length=a.sequence_length, grad_dtype=a.grad_dtype,
                       optimizer=a.optimizer, momentum_dtype=a.momentum_dtype,
                       offload_optimizer_state=a.offload_optimizer_state, resident_state_gb=a.resident_state_gb,
+                      reshard_params=a.reshard_params,
                       ep_backend=a.ep_backend, fp8_training=a.fp8_training)
     dims = ModelDims.from_json(a.model)
     ranks = [a.pp_rank] if a.pp_rank >= 0 else list(range(par.pp))

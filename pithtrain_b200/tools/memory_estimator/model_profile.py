@@ -37,6 +37,7 @@ class ParallelCfg:
     ep_backend: str = "fused"  # "fused" (symmetric buffers) or "nccl"
     fp8_training: bool = False  # block-scaled e4m3 forward / input-gradient GEMMs: cached quantised weight copies
     capacity_factor: Optional[float] = None
+    reshard_params: bool = False  # DistributedCfg.reshard_params: owned parameters in a buffer of their own
 
     @property
     def world(self) -> int:
@@ -210,6 +211,10 @@ def static_memory(dims: ModelDims, par: ParallelCfg, pp_rank: int) -> StaticMemo
     gb, mb = DTYPE_BYTES[par.grad_dtype], DTYPE_BYTES[par.momentum_dtype]
     out = StaticMemory()
     out.params = 2 * (dense + expert)
+    if par.reshard_params:
+        # while a step runs the flat buffers are whole and the owned parameters exist a second time; between steps only
+        # the owned copy stays (the estimate is the peak inside a step)
+        out.params += int(2 * (dense / (par.dp * par.cp * par.ep) + expert / (par.dp * par.cp)))
     out.grads = gb * (dense + expert)
     if par.fp8_training:
         # one e4m3 byte per element in each orientation (forward reads W, the input gradient reads W^T), cached for the
