@@ -37,11 +37,21 @@ def fp8cast_rowwise_colwise(x: torch.Tensor) -> Four:
 
 def fp8cast_rowwise_kmajor(x: torch.Tensor, grouped_mm_offs: torch.Tensor) -> Four:
     """Row-wise cast plus the column-wise payload laid out group by group as ``[N, rows_g]`` blocks in one flat
-    tensor, with the column-wise scales transposed to ``[N, M/128]`` (the reference's grouped-wgrad operand)."""
+    ``[M * N]`` tensor, with the column-wise scales transposed to ``[N, M/128]`` (the reference's grouped-wgrad operand).
+    ``grouped_mm_offs`` holds the cumulative row counts; rows past the last one (if any) form a trailing block.
+    Nothing is read back to the host: the destination of every element is computed on the device."""
     tok, tok_s, ch, ch_s = fp8cast_rowwise_colwise(x)
-    ends = [0] + grouped_mm_offs.tolist()
-    flat = torch.cat([ch[a:b].t().contiguous().view(torch.uint8).reshape(-1) for a, b in zip(ends[:-1], ends[1:])]) \
-        if len(ends) > 1 else ch.view(torch.uint8).reshape(-1)
+    M, N = x.shape
+    offs = grouped_mm_offs.to(device=x.device, dtype=torch.int64)
+    rows = torch.arange(M, device=x.device, dtype=torch.int64)
+    ends = torch.cat([offs, torch.full((1,), M, device=x.device, dtype=torch.int64)])
+    g = torch.searchsorted(ends, rows, right=True)            # block of every row
+    starts = torch.cat([torch.zeros(1, device=x.device, dtype=torch.int64), ends])[g]
+    lens = ends[g.clamp(max=ends.numel() - 1)] - starts
+    # element (r, n) of block [start, start + len) goes to start * N + n * len + (r - start)
+    dest = (starts * N + rows - starts).unsqueeze(1) + torch.arange(N, device=x.device, dtype=torch.int64).unsqueeze(0) * lens.unsqueeze(1)
+    flat = torch.empty(M * N, dtype=torch.uint8, device=x.device)
+    flat[dest.reshape(-1)] = ch.view(torch.uint8).reshape(-1)
     return tok, tok_s, flat.view(torch.float8_e4m3fn), ch_s.t().contiguous()
 
 

@@ -134,3 +134,9 @@ def test_reference_named_quantiser_wrappers():
     _, _, flat, km_s = DQ.fp8cast_rowwise_kmajor(x, offs)
     assert flat.shape == (256 * 300,) and km_s.shape == (300, 2)
     assert torch.equal(flat[:128 * 300].view(300, 128).float(), ch[:128].t().float())
+    assert torch.equal(flat[128 * 300:].view(300, 128).float(), ch[128:].t().float())
+    # uneven groups, an empty one, and rows past the last offset (a trailing block)
+    _, _, flat2, _ = DQ.fp8cast_rowwise_kmajor(x, torch.tensor([128, 128, 128 + 64], dtype=torch.int32))
+    assert torch.equal(flat2[:128 * 300].view(300, 128).float(), ch[:128].t().float())
+    assert torch.equal(flat2[128 * 300:192 * 300].view(300, 64).float(), ch[128:192].t().float())
+    assert torch.equal(flat2[192 * 300:].view(300, 64).float(), ch[192:].t().float())
