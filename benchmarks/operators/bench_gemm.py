@@ -32,7 +32,10 @@ def dense(M, N, K):
     x, w, dy = rand_bf16(M, K), rand_bf16(N, K), rand_bf16(M, N)
     gw = torch.zeros(N, K, device="cuda", dtype=torch.bfloat16)
     fl = 2 * M * N * K
-    line(f"dense fwd  NT {M}x{N}x{K} tcgen05", fl, bench(lambda: G.gemm_nt(x, w)))
+    line(f"dense fwd  NT {M}x{N}x{K} tcgen05 (CTA pairs, default)", fl, bench(lambda: G.gemm_nt(x, w)))
+    G.USE_2CTA = False
+    line(f"dense fwd  NT {M}x{N}x{K} tcgen05 (single CTA)", fl, bench(lambda: G.gemm_nt(x, w)))
+    G.USE_2CTA = True
     line(f"dense fwd  NT {M}x{N}x{K} cuBLAS", fl, bench(lambda: torch.matmul(x, w.t())))
     line(f"dense dgrad NN {M}x{N}x{K} tcgen05", fl, bench(lambda: G.gemm_nn(dy, w)))
     line(f"dense dgrad NN {M}x{N}x{K} cuBLAS", fl, bench(lambda: torch.matmul(dy, w)))
@@ -54,6 +57,11 @@ def grouped(E, rows, H, I2):
         line(f"grouped fwd   {tag} F.grouped_mm", fl, bench(lambda: F.grouped_mm(xs, w.transpose(1, 2), offs=offs[1:])))
     line(f"grouped dgrad {tag} tcgen05", fl, bench(lambda: G.grouped_gemm_nn(dy, w, offs, out=dx)))
     line(f"grouped wgrad {tag} tcgen05 (TMA reduce-add)", fl, bench(lambda: G.grouped_gemm_tn(dy, xs, offs, gw)))
+    gw32 = torch.zeros(E, I2, H, device="cuda", dtype=torch.float32)
+    line(f"grouped wgrad {tag} fp32 accumulators, two launches", 2 * fl,
+         bench(lambda: (G.grouped_gemm_tn(dy, xs, offs, gw32, accumulate=True), G.grouped_gemm_tn(dy, xs, offs, gw32, accumulate=True))))
+    line(f"grouped wgrad {tag} fp32 accumulators, paired launch", 2 * fl,
+         bench(lambda: G.grouped_gemm_tn_pair(dy, xs, offs, dy, xs, offs, gw32)))
     if hasattr(F, "grouped_mm"):
         def lib_wgrad():
             gw.add_(F.grouped_mm(dy.t(), xs, offs=offs[1:]))
