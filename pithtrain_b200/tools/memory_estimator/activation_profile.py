@@ -37,7 +37,10 @@ def token_counts(dims: ModelDims, par: ParallelCfg, imbalance: float = 1.0) -> T
             cap = min(worst, (want + 127) // 128 * 128)
     else:
         cap = recv
-    return TokenCounts(T=T, recv=min(recv, worst), sorted_rows=pairs + 16 * (dims.E // ep), recv_capacity=cap)
+    # the expert-side buffers (sorted row index, gate/up output) are allocated for every received row hitting k local
+    # experts: nothing is read back to the host to size them by what actually arrived
+    sorted_rows = (cap * k if ep > 1 else pairs) + 16 * (dims.E // ep)
+    return TokenCounts(T=T, recv=min(recv, worst), sorted_rows=sorted_rows, recv_capacity=cap)
 
 
 @dataclass
